@@ -5,7 +5,8 @@ Upstream keeps one pool of 32 KiB pages, each holding 16 tokens of one layer
 (K[16][512] then V[16][512]), and a block table per slot and layer
 (paged_attention/src/config.h:181-193, paged_attention/src/engine.cu:176-254).
 Here a page id covers every layer of its group: the group's tensor is
-[entries, 2, num_pages, kv_heads, page_size, head_dim], so a (page, head) tile is one
+[entries, planes, num_pages, kv_heads, page_size, head_dim] (planes: keys and values, or
+one plane for a mixer that keeps a single latent row per token), so a (page, head) tile is one
 contiguous run and the block table is one row per request.  Mixers with equal
 needs share a group; mixers with other needs (another head shape, a window) get a
 group, a pool and tables of their own.
@@ -41,7 +42,7 @@ class PagedCache:
             if cache_of[i] is not None or not isinstance(spec, PagedKVSpec):
                 self.entry_group.append(None)
                 continue
-            key = (spec.num_kv_heads, spec.head_dim, spec.window or 0)
+            key = (spec.num_kv_heads, spec.head_dim, spec.window or 0, int(spec.planes))
             if key not in group_keys:
                 group_keys.append(key)
                 counts.append(0)
@@ -60,7 +61,7 @@ class PagedCache:
         if not group_keys:
             # A model without paged mixers still gets one (empty) group, so that the
             # manager, the tables and the scheduler work unchanged.
-            self.group_keys = [(0, 0, 0)]
+            self.group_keys = [(0, 0, 0, 2)]
             self.group_entries = [0]
         self.manager = host.CacheManager(
             [host.GroupSpec(self.page_size, key[2]) for key in self.group_keys],
@@ -72,8 +73,8 @@ class PagedCache:
         if allocate:
             # One page and one slot more than the manager hands out: padding rows of a
             # fixed-shape (graph) batch write there.
-            for (nkv, d, _w), n in zip(self.group_keys, self.group_entries):
-                self.kv.append(torch.zeros((max(n, 0), 2, self.num_pages + 1, nkv, self.page_size, d),
+            for (nkv, d, _w, planes), n in zip(self.group_keys, self.group_entries):
+                self.kv.append(torch.zeros((max(n, 0), planes, self.num_pages + 1, nkv, self.page_size, d),
                                            dtype=dtype, device=self.device) if n else None)
             for i, spec in enumerate(entry_specs):
                 if isinstance(spec, SlotStateSpec) and cache_of[i] is None:
@@ -90,12 +91,13 @@ class PagedCache:
 
     def bytes_per_page(self) -> int:
         esz = torch.empty((), dtype=self.dtype).element_size()
-        return sum(n * 2 * nkv * self.page_size * d * esz for (nkv, d, _), n in zip(self.group_keys, self.group_entries))
+        return sum(n * planes * nkv * self.page_size * d * esz
+                   for (nkv, d, _, planes), n in zip(self.group_keys, self.group_entries))
 
     @staticmethod
     def bytes_per_token(entry_specs, cache_of, dtype) -> int:
         esz = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * s.num_kv_heads * s.head_dim * esz for i, s in enumerate(entry_specs)
+        return sum(s.planes * s.num_kv_heads * s.head_dim * esz for i, s in enumerate(entry_specs)
                    if isinstance(s, PagedKVSpec) and cache_of[i] is None)
 
     def binding(self, entry: int):
@@ -105,7 +107,7 @@ class PagedCache:
         if isinstance(spec, PagedKVSpec):
             g, idx = self.entry_group[owner]
             t = self.kv[g]
-            return PagedKVBinding(k=t[idx, 0], v=t[idx, 1], group=g, page_size=self.page_size,
+            return PagedKVBinding(k=t[idx, 0], v=t[idx, 1] if t.shape[1] > 1 else None, group=g, page_size=self.page_size,
                                   write=(src is None))
         if isinstance(spec, SlotStateSpec):
             return SlotStateBinding(state=self.states[owner], write=(src is None))

@@ -11,10 +11,13 @@ import torch
 @dataclass(frozen=True)
 class PagedKVSpec:
     """Keys and values that grow with the sequence, kept in pages.  ``window``: only
-    the newest ``window`` keys are ever read, older pages may be given back."""
+    the newest ``window`` keys are ever read, older pages may be given back.
+    ``planes``: 2 keeps keys and values; 1 keeps a single row per token and head (a mixer
+    whose keys and values are both read from one cached latent)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -27,11 +30,12 @@ class SlotStateSpec:
 @dataclass
 class PagedKVBinding:
     """A schedule entry's view of its pages: ``k`` and ``v`` are
-    [num_pages, num_kv_heads, page_size, head_dim]; the block tables of the step's
+    [num_pages, num_kv_heads, page_size, head_dim] (``v`` is None for a group that keeps one
+    plane); the block tables of the step's
     requests are ``batch.block_tables[group]``.  ``write`` is False for an entry that
     reads another entry's cache."""
     k: torch.Tensor
-    v: torch.Tensor
+    v: Optional[torch.Tensor]
     group: int
     page_size: int
     write: bool = True

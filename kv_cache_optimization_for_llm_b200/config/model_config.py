@@ -182,6 +182,89 @@ class LlamaConfig:
         return d
 
 
+@dataclass(frozen=True)
+class RezusunLayerConfig:
+    """One entry of ``layers``: the mixer's kind and sizes, and the feed-forward (None: the
+    layer has only its mixer)."""
+    type: str
+    mixer: Mapping[str, Any]
+    mlp: Optional[Mapping[str, Any]]
+
+
+_REZUSUN_MIXER_KEYS = {
+    "latent_attention": ("heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank", "scale", "rot"),
+    "general_delta": ("heads", "dim"),
+    "channel_delta": ("heads", "kv_heads", "dim", "vdim", "conv"),
+}
+
+
+@dataclass(frozen=True)
+class RezusunConfig:
+    """The keys of a Rezusun config.json: ``vocab``, ``width``, ``norm.eps``, ``layers`` (each with
+    ``type``, ``mixer`` and ``mlp``) and ``loop`` (layers start .. stop - 1 run ``times`` times in a
+    row).  Sizes that the file leaves to the tensors' shapes (ranks of the low-rank branches)
+    are read from the checkpoint when the model is described."""
+    architecture: str
+    vocab: int
+    width: int
+    norm_eps: float
+    layers: Tuple[RezusunLayerConfig, ...]
+    loop: Optional[Tuple[int, int, int]]
+    max_position_embeddings: int
+    eos_token_ids: Tuple[int, ...] = field(default_factory=tuple)
+
+    @classmethod
+    def from_dict(cls, d: Mapping[str, Any]) -> "RezusunConfig":
+        norm = d.get("norm") or {}
+        layers = []
+        for i, entry in enumerate(d.get("layers") or []):
+            kind = entry.get("type")
+            if kind not in _REZUSUN_MIXER_KEYS:
+                raise ConfigError(f"config.json: layer {i} has a mixer of type {kind!r}; known: "
+                                  + ", ".join(sorted(_REZUSUN_MIXER_KEYS)))
+            mixer = entry.get("mixer") or {}
+            for key in _REZUSUN_MIXER_KEYS[kind]:
+                if mixer.get(key) is None:
+                    raise ConfigError(f"config.json: layer {i} ({kind}): mixer key {key!r} is missing")
+            if kind == "latent_attention":
+                for key in ("base", "dims"):
+                    if mixer["rot"].get(key) is None:
+                        raise ConfigError(f"config.json: layer {i}: rot.{key} is missing")
+            mlp = entry.get("mlp")
+            if mlp is not None:
+                if mlp.get("kind") != "dense":
+                    raise ConfigError(f"config.json: layer {i}: a feed-forward of kind {mlp.get('kind')!r} is not known "
+                                      "(known: 'dense')")
+                _need(mlp, "ff", int)
+            layers.append(RezusunLayerConfig(str(kind), dict(mixer), dict(mlp) if mlp is not None else None))
+        if not layers:
+            raise ConfigError("config.json: 'layers' is missing or empty")
+        loop = d.get("loop")
+        loop_t = None
+        if loop:
+            loop_t = (_need(loop, "start", int), _need(loop, "stop", int), _need(loop, "times", int))
+            a, b, n = loop_t
+            if not (0 <= a <= b <= len(layers)) or n < 1:
+                raise ConfigError(f"config.json: loop {dict(loop)} does not fit {len(layers)} layers")
+        eos = d.get("eos_token_id")
+        eos_ids = () if eos is None else (tuple(int(e) for e in eos) if isinstance(eos, (list, tuple)) else (int(eos),))
+        cfg = cls(architecture=str(d.get("architecture") or (d.get("architectures") or ["Rezusun"])[0]),
+                  vocab=_need(d, "vocab", int), width=_need(d, "width", int), norm_eps=_need(norm, "eps", float),
+                  layers=tuple(layers), loop=loop_t,
+                  max_position_embeddings=int(d.get("max_position_embeddings") or 131072), eos_token_ids=eos_ids)
+        if cfg.vocab < 1 or cfg.width < 1 or not cfg.norm_eps > 0:
+            raise ConfigError("config.json: vocab and width must be positive and norm.eps above zero")
+        return cfg
+
+    def layer_order(self):
+        """Indices of the layers in the order they run."""
+        n = len(self.layers)
+        if self.loop is None:
+            return list(range(n))
+        a, b, times = self.loop
+        return list(range(a)) + list(range(a, b)) * times + list(range(b, n))
+
+
 def read_config_json(model_dir) -> dict:
     path = Path(model_dir) / "config.json"
     if not path.exists():

@@ -1,0 +1,344 @@
+// Mixers that carry a matrix state per head from token to token (the delta-rule family).
+//
+// Every member updates a state S [Dk, Dv] per head and token as
+//     S <- diag(d) S - p (x^T S) + k c^T          (both products read the state before the token)
+// and reads  o = S^T r  afterwards.  What differs between members is how d, p, x, k, c, r
+// follow from the projections of the token:
+//   * MODE_GENERAL: decay d = exp(-e^{-1/2} sigmoid(z_d + b_d)) per key channel, removal along
+//     the unit key u = k / sqrt(|k|^2 + 1e-6) at the rate a = sigmoid(z_a + b_a):  p = a * u,
+//     x = u, c = v, read-out by r.
+//   * MODE_GATED: decay g = exp(-exp(A_h) softplus(z_d + b_d)) per key channel, unit q and k
+//     (q also times Dk^-1/2), write strength beta = sigmoid(z_b) per head; decaying first and
+//     then correcting the state's prediction for k is the same update with d = g, p = beta k,
+//     x = k * g, c = beta v, read-out by q.
+// Columns of S are independent of each other, so a thread owns a quarter of one column (the
+// key channels {i : (i / 4) % 4 == lane part}) in registers for the whole run of tokens.  With
+// y = r * d the read-out is  o_j = y.s_j - (x.s_j)(p.r) + c_j (k.r)  over the state before the
+// token, so one round of shuffles per token serves both the update and the read-out.
+//
+// A block owns one (head, request): it walks the request's tokens of this step in chunks of
+// 16: all warps turn the chunk's projections into the float32 vectors above (one warp per
+// token), then every thread steps through the chunk, then the warps finish the chunk's
+// outputs (RMS over the head, weight, sigmoid gate).  The state is read from the request's
+// slot at the start (zero when the request starts at position 0) and written back at the end.
+// Everything but the projections is float32.  A token's result does not depend on how the
+// request was cut into steps: each token is prepared alone and the scan is sequential.
+//
+// Also here: the short causal convolution with SiLU in front of such a mixer, whose last
+// inputs are part of the request's state.
+#include "common.cuh"
+
+enum DeltaMode { MODE_GENERAL = 0, MODE_GATED = 1 };
+
+constexpr int kChunk = 16;
+
+struct DeltaArgs {
+  const void* r; int ld_r;          // read-out projection, [T, G * Dk] (q for MODE_GATED)
+  const void* k; int ld_k;          // key projection, [T, G * Dk]
+  const void* v; int ld_v;          // value projection, [T, H * Dv]
+  const void* gate; int ld_gate;    // output gate before its sigmoid, [T, H * Dv]
+  const void* decay; int ld_decay;  // z_d, [T, H * Dk]
+  const void* aux; int ld_aux;      // MODE_GENERAL: z_a [T, H * Dk]; MODE_GATED: z_b [T, H]
+  const float* decay_bias;          // b_d [H * Dk]
+  const float* aux_bias;            // MODE_GENERAL: b_a [H * Dk]
+  const float* head_rate;           // MODE_GATED: A [H]
+  const float* norm_w;              // [H * Dv] or [Dv]
+  int norm_per_head;
+  float* state;                     // [slots, H, Dv, 4 KPL] at slot_stride floats per slot
+  long long slot_stride;
+  void* out; int ld_out;            // [T, H * Dv]
+  const int* q_start;               // [R + 1] first token row of each request's run
+  const int* req_start;             // [R] position of the run's first token
+  const int* slots;                 // [R]
+  int H, G, Dk, Dv;
+  float eps;
+};
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+template <typename T, int KPL, int MODE>
+__global__ void delta_scan_kernel(const DeltaArgs a) {
+  constexpr int DKP = 4 * KPL;
+  extern __shared__ float4 smem4[];
+  float* smem = reinterpret_cast<float*>(smem4);
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.x, req = blockIdx.y;
+  const int Dk = a.Dk, Dv = a.Dv;
+  const int dvp = (Dv + 3) & ~3;
+  const int tok_floats = 5 * DKP + 2 * dvp + 4;      // d, p, x, k, y | c | o | (p.r, k.r)
+  const int t0 = a.q_start[req], t1 = a.q_start[req + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int col = threadIdx.x >> 2, part = threadIdx.x & 3;
+  const int hk = h / (a.H / a.G);
+  const T* rp = static_cast<const T*>(a.r);
+  const T* kp = static_cast<const T*>(a.k);
+  const T* vp = static_cast<const T*>(a.v);
+  const T* gp = static_cast<const T*>(a.gate);
+  const T* dp = static_cast<const T*>(a.decay);
+  const T* xp = static_cast<const T*>(a.aux);
+  T* outp = static_cast<T*>(a.out);
+
+  float s[KPL];
+  float* my_state = a.state + (size_t)a.slots[req] * a.slot_stride + ((size_t)h * Dv + col) * DKP;
+  const bool fresh = a.req_start[req] == 0;
+#pragma unroll
+  for (int e4 = 0; e4 < KPL / 4; ++e4) {
+    float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!fresh && col < Dv) v4 = *reinterpret_cast<const float4*>(my_state + (e4 * 4 + part) * 4);
+    s[e4 * 4 + 0] = v4.x; s[e4 * 4 + 1] = v4.y; s[e4 * 4 + 2] = v4.z; s[e4 * 4 + 3] = v4.w;
+  }
+  const float rate = MODE == MODE_GATED ? expf(a.head_rate[h]) : 0.60653065971263342f;   // e^{-1/2}
+  const float q_scale = rsqrtf((float)Dk);
+
+  for (int base = t0; base < t1; base += kChunk) {
+    const int n = min(kChunk, t1 - base);
+    // ---- the chunk's vectors, one warp per token
+    for (int c = warp; c < n; c += nwarps) {
+      const int t = base + c;
+      float* tok = smem + (size_t)c * tok_floats;
+      float kr_[DKP / 32 > 0 ? DKP / 32 : 1], rr_[DKP / 32 > 0 ? DKP / 32 : 1];
+      float ksum = 0.f, rsum = 0.f;
+#pragma unroll
+      for (int u = 0; u < (DKP + 31) / 32; ++u) {
+        const int i = u * 32 + lane;
+        float kv = 0.f, rv = 0.f;
+        if (i < Dk) {
+          kv = to_f32(kp[(size_t)t * a.ld_k + hk * Dk + i]);
+          rv = to_f32(rp[(size_t)t * a.ld_r + hk * Dk + i]);
+        }
+        kr_[u] = kv; rr_[u] = rv;
+        ksum += kv * kv; rsum += rv * rv;
+      }
+      ksum = warp_sum(ksum);
+      rsum = warp_sum(rsum);
+      const float kinv = 1.0f / sqrtf(ksum + 1e-6f);
+      const float rinv = MODE == MODE_GATED ? q_scale / sqrtf(rsum + 1e-6f) : 1.0f;
+      float beta = 1.f;
+      if (MODE == MODE_GATED) beta = sigmoidf_(to_f32(xp[(size_t)t * a.ld_aux + h]));
+      float pr = 0.f, kr = 0.f;
+#pragma unroll
+      for (int u = 0; u < (DKP + 31) / 32; ++u) {
+        const int i = u * 32 + lane;
+        if (i >= DKP) continue;
+        float d = 0.f, p = 0.f, x = 0.f, kk = 0.f, y = 0.f;
+        if (i < Dk) {
+          const float zd = to_f32(dp[(size_t)t * a.ld_decay + h * Dk + i]) + a.decay_bias[h * Dk + i];
+          if (MODE == MODE_GENERAL) {
+            const float unit = kr_[u] * kinv;
+            const float rem = sigmoidf_(to_f32(xp[(size_t)t * a.ld_aux + h * Dk + i]) + a.aux_bias[h * Dk + i]);
+            d = expf(-rate * sigmoidf_(zd));
+            p = rem * unit; x = unit; kk = kr_[u]; y = rr_[u] * d;
+            pr += p * rr_[u]; kr += kk * rr_[u];
+          } else {
+            const float kn = kr_[u] * kinv, qn = rr_[u] * rinv;
+            d = expf(-rate * softplusf_(zd));
+            p = beta * kn; x = kn * d; kk = kn; y = qn * d;
+            kr += kn * qn;
+          }
+        }
+        tok[i] = d; tok[DKP + i] = p; tok[2 * DKP + i] = x; tok[3 * DKP + i] = kk; tok[4 * DKP + i] = y;
+      }
+      pr = warp_sum(pr);
+      kr = warp_sum(kr);
+      if (MODE == MODE_GATED) pr = beta * kr;
+      if (lane == 0) { tok[5 * DKP + 2 * dvp] = pr; tok[5 * DKP + 2 * dvp + 1] = kr; }
+    }
+    // the chunk's column values c_j
+    for (int idx = threadIdx.x; idx < n * dvp; idx += blockDim.x) {
+      const int c = idx / dvp, j = idx - c * dvp;
+      const int t = base + c;
+      float cv = 0.f;
+      if (j < Dv) {
+        cv = to_f32(vp[(size_t)t * a.ld_v + h * Dv + j]);
+        if (MODE == MODE_GATED) cv *= sigmoidf_(to_f32(xp[(size_t)t * a.ld_aux + h]));
+      }
+      smem[(size_t)c * tok_floats + 5 * DKP + j] = cv;
+    }
+    __syncthreads();
+    // ---- the scan over the chunk
+    if (col < dvp) {
+      for (int c = 0; c < n; ++c) {
+        const float* tok = smem + (size_t)c * tok_floats;
+        const float4* D4 = reinterpret_cast<const float4*>(tok);
+        const float4* P4 = reinterpret_cast<const float4*>(tok + DKP);
+        const float4* X4 = reinterpret_cast<const float4*>(tok + 2 * DKP);
+        const float4* K4 = reinterpret_cast<const float4*>(tok + 3 * DKP);
+        const float4* Y4 = reinterpret_cast<const float4*>(tok + 4 * DKP);
+        float dx = 0.f, dy = 0.f;
+#pragma unroll
+        for (int e4 = 0; e4 < KPL / 4; ++e4) {
+          const float4 xv = X4[e4 * 4 + part], yv = Y4[e4 * 4 + part];
+          dx = fmaf(xv.x, s[e4 * 4 + 0], dx); dx = fmaf(xv.y, s[e4 * 4 + 1], dx);
+          dx = fmaf(xv.z, s[e4 * 4 + 2], dx); dx = fmaf(xv.w, s[e4 * 4 + 3], dx);
+          dy = fmaf(yv.x, s[e4 * 4 + 0], dy); dy = fmaf(yv.y, s[e4 * 4 + 1], dy);
+          dy = fmaf(yv.z, s[e4 * 4 + 2], dy); dy = fmaf(yv.w, s[e4 * 4 + 3], dy);
+        }
+        dx += __shfl_xor_sync(0xffffffffu, dx, 1); dy += __shfl_xor_sync(0xffffffffu, dy, 1);
+        dx += __shfl_xor_sync(0xffffffffu, dx, 2); dy += __shfl_xor_sync(0xffffffffu, dy, 2);
+        const float cj = tok[5 * DKP + col];
+        const float pr = tok[5 * DKP + 2 * dvp], kr = tok[5 * DKP + 2 * dvp + 1];
+        if (part == 0) smem[(size_t)c * tok_floats + 5 * DKP + dvp + col] = dy - dx * pr + cj * kr;
+#pragma unroll
+        for (int e4 = 0; e4 < KPL / 4; ++e4) {
+          const float4 dv = D4[e4 * 4 + part], pv = P4[e4 * 4 + part], kv = K4[e4 * 4 + part];
+          s[e4 * 4 + 0] = fmaf(dv.x, s[e4 * 4 + 0], fmaf(kv.x, cj, -pv.x * dx));
+          s[e4 * 4 + 1] = fmaf(dv.y, s[e4 * 4 + 1], fmaf(kv.y, cj, -pv.y * dx));
+          s[e4 * 4 + 2] = fmaf(dv.z, s[e4 * 4 + 2], fmaf(kv.z, cj, -pv.z * dx));
+          s[e4 * 4 + 3] = fmaf(dv.w, s[e4 * 4 + 3], fmaf(kv.w, cj, -pv.w * dx));
+        }
+      }
+    }
+    __syncthreads();
+    // ---- the chunk's outputs: RMS over the head, weight, sigmoid gate
+    for (int c = warp; c < n; c += nwarps) {
+      const int t = base + c;
+      const float* o = smem + (size_t)c * tok_floats + 5 * DKP + dvp;
+      float ss = 0.f;
+      for (int j = lane; j < Dv; j += 32) ss += o[j] * o[j];
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)Dv + a.eps);
+      for (int j = lane; j < Dv; j += 32) {
+        const float w = a.norm_w[(a.norm_per_head ? h * Dv : 0) + j];
+        const float g = sigmoidf_(to_f32(gp[(size_t)t * a.ld_gate + h * Dv + j]));
+        outp[(size_t)t * a.ld_out + h * Dv + j] = from_f32<T>(o[j] * inv * w * g);
+      }
+    }
+    __syncthreads();
+  }
+  if (col < Dv) {
+#pragma unroll
+    for (int e4 = 0; e4 < KPL / 4; ++e4)
+      *reinterpret_cast<float4*>(my_state + (e4 * 4 + part) * 4) =
+          make_float4(s[e4 * 4 + 0], s[e4 * 4 + 1], s[e4 * 4 + 2], s[e4 * 4 + 3]);
+  }
+}
+
+// Key channels per quarter column for a key size: the smallest of 4, 8, 16, 32 whose fourfold
+// holds Dk (0: refused).  The state's rows are padded to four times this.
+static int delta_kpl(int Dk) {
+  for (int k = 4; k <= 32; k *= 2)
+    if (4 * k >= Dk) return k;
+  return 0;
+}
+
+KVB_EXPORT int kvb_delta_key_pad(int Dk) { return Dk >= 1 ? 4 * delta_kpl(Dk) : 0; }
+
+template <typename T, int KPL, int MODE>
+static int launch_scan(const DeltaArgs& a, int R, cudaStream_t stream) {
+  const int dvp = (a.Dv + 3) & ~3;
+  const int threads = ((4 * dvp + 31) / 32) * 32;
+  const size_t smem = (size_t)kChunk * (5 * 4 * KPL + 2 * dvp + 4) * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<T, KPL, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  kvb_launch(delta_scan_kernel<T, KPL, MODE>, dim3(a.H, R), dim3(threads), smem, stream, a);
+  return kvb_launch_result();
+}
+
+template <typename T, int MODE>
+static int launch_scan_kpl(const DeltaArgs& a, int R, cudaStream_t stream) {
+  switch (delta_kpl(a.Dk)) {
+    case 4: return launch_scan<T, 4, MODE>(a, R, stream);
+    case 8: return launch_scan<T, 8, MODE>(a, R, stream);
+    case 16: return launch_scan<T, 16, MODE>(a, R, stream);
+    case 32: return launch_scan<T, 32, MODE>(a, R, stream);
+  }
+  return KVB_ERR_BAD_SIZE;
+}
+
+// Refuses: Dk > 128, Dv > 256, Dv > 128 together with Dk > 64 (a thread's quarter column would
+// not stay in registers), heads that do not group evenly.
+KVB_EXPORT int kvb_delta_scan(const DeltaArgs* args, int mode, int R, int dtype, cudaStream_t stream) {
+  const DeltaArgs& a = *args;
+  if (R <= 0) return 0;
+  if (a.Dk < 1 || a.Dk > 128 || a.Dv < 1 || a.Dv > 256 || (a.Dk > 64 && a.Dv > 128)) return KVB_ERR_BAD_SIZE;
+  if (a.G < 1 || a.H % a.G || R > 65535) return KVB_ERR_BAD_SIZE;
+  if (mode != MODE_GENERAL && mode != MODE_GATED) return KVB_ERR_BAD_SIZE;
+  if (mode == MODE_GENERAL) {
+    KVB_DISPATCH_DTYPE(dtype, T, return (launch_scan_kpl<T, MODE_GENERAL>(a, R, stream)));
+  } else {
+    KVB_DISPATCH_DTYPE(dtype, T, return (launch_scan_kpl<T, MODE_GATED>(a, R, stream)));
+  }
+  return KVB_ERR_BAD_DTYPE;
+}
+
+// ---------------------------------------------------------------- short causal convolution + SiLU
+// out[t, c] = silu( sum_j w[c, j] * in[p - (taps - 1) + j, c] ), p the token's position: the last
+// column of w weighs the token itself, inputs before position 0 are zero, and inputs before the
+// step's run come from the request's tail (its last taps - 1 inputs, tail[j] holding position
+// start - (taps - 1) + j).
+template <typename T>
+__device__ __forceinline__ float conv_input(const T* in, int ld, const float* tail, int C, int c, int sp, int start,
+                                            int row0, int taps) {
+  if (sp < 0) return 0.f;
+  if (sp >= start) return to_f32(in[(size_t)(row0 + sp - start) * ld + c]);
+  return tail[(size_t)(sp - (start - (taps - 1))) * C + c];
+}
+
+template <typename T>
+__global__ void conv_silu_kernel(const T* __restrict__ in, int ld, const float* __restrict__ w, int taps,
+                                 const float* __restrict__ tails, long long slot_stride, T* __restrict__ out, int C,
+                                 const int* __restrict__ positions, const int* __restrict__ token_req,
+                                 const int* __restrict__ q_start, const int* __restrict__ req_start,
+                                 const int* __restrict__ slots) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int pos = positions[t], r = token_req[t];
+  const int start = req_start[r], row0 = q_start[r];
+  const float* tail = tails + (size_t)slots[r] * slot_stride;
+  float acc = 0.f;
+  for (int j = 0; j < taps; ++j)
+    acc = fmaf(w[(size_t)c * taps + j], conv_input(in, ld, tail, C, c, pos - (taps - 1) + j, start, row0, taps), acc);
+  out[(size_t)t * C + c] = from_f32<T>(acc / (1.0f + expf(-acc)));
+}
+
+// After the convolution: the request's tail becomes the last taps - 1 inputs up to the end of the
+// step's run (older ones move up when the run is shorter than the tail).
+constexpr int kMaxTail = 15;
+template <typename T>
+__global__ void conv_tail_kernel(const T* __restrict__ in, int ld, int taps, float* __restrict__ tails,
+                                 long long slot_stride, int C, const int* __restrict__ q_start,
+                                 const int* __restrict__ req_start, const int* __restrict__ ctx_len,
+                                 const int* __restrict__ slots) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int start = req_start[r], row0 = q_start[r], end = ctx_len[r];
+  float* tail = tails + (size_t)slots[r] * slot_stride;
+  float keep[kMaxTail];
+#pragma unroll
+  for (int j = 0; j < kMaxTail; ++j)
+    if (j < taps - 1) keep[j] = conv_input(in, ld, tail, C, c, end - (taps - 1) + j, start, row0, taps);
+#pragma unroll
+  for (int j = 0; j < kMaxTail; ++j)
+    if (j < taps - 1) tail[(size_t)j * C + c] = keep[j];
+}
+
+// in: [T, >= C] with row stride ld; w [C, taps] float32; tails: the tail of slot 0, slot_stride
+// floats from slot to slot, each [taps - 1, C]; out [T, C] dense.  Refuses taps > 16.
+KVB_EXPORT int kvb_conv_silu(const void* in, int ld, const float* w, int taps, float* tails, long long slot_stride,
+                             void* out, int C, int T_, int R, const int* positions, const int* token_req,
+                             const int* q_start, const int* req_start, const int* ctx_len, const int* slots,
+                             int dtype, cudaStream_t stream) {
+  if (T_ <= 0 || R <= 0) return 0;
+  if (taps < 1 || taps - 1 > kMaxTail || C < 1) return KVB_ERR_BAD_SIZE;
+  const int threads = 128;
+  const int by = (C + threads - 1) / threads;
+  KVB_DISPATCH_DTYPE(dtype, T, {
+    kvb_launch(conv_silu_kernel<T>, dim3(T_, by), dim3(threads), 0, stream, (const T*)in, ld, w, taps,
+               (const float*)tails, slot_stride, (T*)out, C, positions, token_req, q_start, req_start, slots);
+    if (taps > 1)
+      kvb_launch(conv_tail_kernel<T>, dim3(R, by), dim3(threads), 0, stream, (const T*)in, ld, taps, tails, slot_stride,
+                 C, q_start, req_start, ctx_len, slots);
+  });
+  return kvb_launch_result();
+}

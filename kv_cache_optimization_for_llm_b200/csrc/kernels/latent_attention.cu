@@ -1,0 +1,331 @@
+// Attention whose keys and values are up-projections of a small latent per token: only the
+// latent c (RMS-normed, `rank` wide) and one rotated key part shared by all heads (`rot` wide)
+// are cached, as one row of Dc = rank + rot elements per token in the paged cache.
+//
+// The up-projections are moved to the query side: with k_h = U_h c the score q.k_h equals
+// (U_h^T q).c, so every head attends with an "absorbed" query [U_h^T q_plain | q_rot] over the
+// same cached rows, the weighted sum of the latents comes out [rank] wide per head and the
+// value up-projection is applied to it afterwards.  Three kernels:
+//   latent_prep       per token: RMS norm of the query latent, RMS norm of the key/value latent,
+//                     interleaved rotary encoding of the shared key part, cache write
+//   head_gemm         a product per head, out[t, h, :] = W[h] . in[t, h, :]  (absorbs the queries,
+//                     and up-projects the attended latents)
+//   latent_attention  causal softmax attention of all heads over the cached rows, with a sink:
+//                     the denominator also holds exp(sink_h), a key without a value
+// Scores, softmax weights, sums and angles are float32.  Keys are walked in chunks of 32 by
+// absolute position, so a token's result does not depend on how its request was cut into steps,
+// on the rest of the batch or on where its pages lie.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+// ---------------------------------------------------------------- prep
+// d_in [T, ld]: the query latent at column 0 (q_rank wide), the key/value latent at column
+// kv_off (rank wide) followed by the shared key part (rot wide).
+// cq[t] = rms(d_in[t, :q_rank]) * wq;  page row = [ rms(latent) * wkv | rotate(shared part) ].
+// Rotation: pairs (2i, 2i + 1) for i < rdims / 2 turn by cos/sin[pos, i]; the rest passes.
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_prep_kernel(const T* __restrict__ d_in, int ld, int q_rank, int kv_off, int rank, int rot, int rdims,
+                   const float* __restrict__ wq, const float* __restrict__ wkv, float eps,
+                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_len,
+                   const int* __restrict__ positions, const int* __restrict__ token_req,
+                   const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
+                   T* __restrict__ cq, T* __restrict__ pages, int write, int* status) {
+  __shared__ float part[8];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const T* row = d_in + (size_t)t * ld;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x) { const float x = to_f32(row[i]); sq += x * x; }
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) { const float x = to_f32(row[kv_off + i]); sk += x * x; }
+  sq = warp_sum(sq); sk = warp_sum(sk);
+  if (lane == 0) { part[warp] = sq; part[4 + warp] = sk; }
+  __syncthreads();
+  sq = part[0] + part[1] + part[2] + part[3];
+  sk = part[4] + part[5] + part[6] + part[7];
+  const float iq = 1.0f / sqrtf(sq / (float)q_rank + eps), ik = 1.0f / sqrtf(sk / (float)rank + eps);
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+    cq[(size_t)t * q_rank + i] = from_f32<T>(to_f32(row[i]) * iq * wq[i]);
+  if (!write) return;
+  if (pos < 0 || (rdims > 0 && pos >= table_len)) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, KVB_STATUS_BAD_POSITION);
+    return;
+  }
+  const int lp = pos / page_size;
+  const int page = lp < max_pages ? block_table[(size_t)token_req[t] * max_pages + lp] : -1;
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+    return;
+  }
+  T* dst = pages + ((size_t)page * page_size + (pos % page_size)) * (rank + rot);
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32(row[kv_off + i]) * ik * wkv[i]);
+  const int half = rdims >> 1;
+  const T* kr = row + kv_off + rank;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
+    const float u = to_f32(kr[2 * i]), v = to_f32(kr[2 * i + 1]);
+    dst[rank + 2 * i] = from_f32<T>(u * c - v * s);
+    dst[rank + 2 * i + 1] = from_f32<T>(v * c + u * s);
+  }
+  for (int i = rdims + threadIdx.x; i < rot; i += blockDim.x) dst[rank + i] = kr[i];
+}
+
+KVB_EXPORT int kvb_latent_prep(const void* d_in, int ld, int q_rank, int kv_off, int rank, int rot, int rdims,
+                               const float* wq, const float* wkv, float eps, const float* cos_t, const float* sin_t,
+                               int table_len, const int* positions, const int* token_req, const int* block_table,
+                               int max_pages, int page_size, int num_pages, void* cq, void* pages, int write,
+                               int T_, int dtype, int* status, cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (q_rank < 1 || rank < 1 || rot < 0 || rdims < 0 || (rdims & 1) || rdims > rot) return KVB_ERR_BAD_SIZE;
+  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(latent_prep_kernel<T>, dim3(T_), dim3(128), 0, stream, (const T*)d_in, ld,
+                                            q_rank, kv_off, rank, rot, rdims, wq, wkv, eps, cos_t, sin_t, table_len,
+                                            positions, token_req, block_table, max_pages, page_size, num_pages,
+                                            (T*)cq, (T*)pages, write, status)));
+  return kvb_launch_result();
+}
+
+// ---------------------------------------------------------------- a product per head
+// out[t, h * hs_out + n] = sum_k in[t, h * hs_in + k] * W[h, n, k]   for n < N, k < K, h < H.
+// Plain FMA in ascending k with float32 sums: an output does not depend on the number of rows.
+constexpr int HG_BM = 64, HG_BN = 64, HG_BK = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_gemm_kernel(const T* __restrict__ in, int ld_in, int hs_in, const T* __restrict__ W, T* __restrict__ out,
+                 int ld_out, int hs_out, int M, int N, int K) {
+  __shared__ float As[HG_BK][HG_BM + 4];
+  __shared__ float Ws[HG_BK][HG_BN + 4];
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.z;
+  const T* A = in + (size_t)h * hs_in;
+  const T* Wh = W + (size_t)h * N * K;
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * HG_BM, n0 = blockIdx.x * HG_BN;
+  const int tx = tid & 15, ty = tid >> 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  const int lrow = tid >> 2, lk = (tid & 3) * 4;
+  for (int k0 = 0; k0 < K; k0 += HG_BK) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int k = k0 + lk + u;
+      const int am = m0 + lrow, wn = n0 + lrow;
+      As[lk + u][lrow] = (am < M && k < K) ? to_f32(A[(size_t)am * ld_in + k]) : 0.f;
+      Ws[lk + u][lrow] = (wn < N && k < K) ? to_f32(Wh[(size_t)wn * K + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < HG_BK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) out[(size_t)m * ld_out + (size_t)h * hs_out + n] = from_f32<T>(acc[i][j]);
+    }
+  }
+}
+
+KVB_EXPORT int kvb_head_gemm(const void* in, int ld_in, int hs_in, const void* W, void* out, int ld_out, int hs_out,
+                             int M, int N, int K, int H, int dtype, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || H <= 0) return 0;
+  if (K <= 0 || H > 65535) return KVB_ERR_BAD_SIZE;
+  dim3 grid((N + HG_BN - 1) / HG_BN, (M + HG_BM - 1) / HG_BM, H);
+  if (grid.y > 65535) return KVB_ERR_BAD_SIZE;
+  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(head_gemm_kernel<T>, grid, dim3(256), 0, stream, (const T*)in, ld_in, hs_in,
+                                            (const T*)W, (T*)out, ld_out, hs_out, M, N, K)));
+  return kvb_launch_result();
+}
+
+// ---------------------------------------------------------------- attention over the cached rows
+// A block takes one query token and up to kLatWarps heads, one head per warp.  The block loads a
+// chunk of 32 cached rows into shared memory once for all its heads; a lane scores one key
+// (dot over Dc), the warp keeps a running maximum and sum that start from the sink
+// (m = sink_h, l = 1: the sink counts once and has no value), and lanes then own value dims.
+constexpr int kLatWarps = 8;
+
+template <typename T> struct Word;     // a 4-byte word of shared memory: 1 float or 2 bfloat16
+template <> struct Word<float> {
+  static constexpr int N = 1;
+  static __device__ __forceinline__ float dot(const float* q, unsigned w) { return q[0] * __uint_as_float(w); }
+};
+template <> struct Word<__nv_bfloat16> {
+  static constexpr int N = 2;
+  static __device__ __forceinline__ float dot(const float* q, unsigned w) {
+    return fmaf(q[1], __uint_as_float(w & 0xffff0000u), q[0] * __uint_as_float(w << 16));
+  }
+};
+
+template <typename T, int NR>
+__global__ void __launch_bounds__(kLatWarps * 32)
+latent_attention_kernel(const T* __restrict__ q_abs, int ld_qa, int hs_qa,     // [T, H, rank] absorbed plain part
+                        const T* __restrict__ q_raw, int ld_q, int hs_q,        // rotated part before rotation, rot wide
+                        const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_len, int rdims,
+                        const T* __restrict__ pages, const int* __restrict__ block_table, int max_pages,
+                        int page_size, int num_pages, const int* __restrict__ positions,
+                        const int* __restrict__ token_req, const float* __restrict__ sink, float scale,
+                        T* __restrict__ out, int ld_out, int hs_out, int H, int rank, int rot, int* status) {
+  extern __shared__ unsigned lat_smem[];
+  constexpr int EW = Word<T>::N;
+  const int Dc = rank + rot;
+  const int words = Dc / EW;
+  const int stride = words | 1;                       // odd: lanes reading one column of a chunk hit 32 banks
+  float* q_s = reinterpret_cast<float*>(lat_smem);    // [kLatWarps][Dc]
+  unsigned* k_s = lat_smem + kLatWarps * Dc;          // [32][stride]
+  __shared__ long long row_of[32];                    // element offset of each key's row, -1: not readable
+
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y * kLatWarps + warp;
+  const bool live = h < H;
+  const int pos = positions[t];
+  const int* table = block_table + (size_t)token_req[t] * max_pages;
+  const bool bad_pos = rdims > 0 && (pos < 0 || pos >= table_len);
+  if (bad_pos && threadIdx.x == 0) atomicCAS(status, 0, KVB_STATUS_BAD_POSITION);
+
+  if (live) {
+    float* q = q_s + warp * Dc;
+    for (int i = lane; i < rank; i += 32) q[i] = to_f32(q_abs[(size_t)t * ld_qa + (size_t)h * hs_qa + i]);
+    const T* qr = q_raw + (size_t)t * ld_q + (size_t)h * hs_q;
+    const int half = rdims >> 1;
+    for (int i = lane; i < half; i += 32) {
+      float c = 1.f, s = 0.f;
+      if (!bad_pos) { c = cos_t[(size_t)pos * half + i]; s = sin_t[(size_t)pos * half + i]; }
+      const float u = to_f32(qr[2 * i]), v = to_f32(qr[2 * i + 1]);
+      q[rank + 2 * i] = u * c - v * s;
+      q[rank + 2 * i + 1] = v * c + u * s;
+    }
+    for (int i = rdims + lane; i < rot; i += 32) q[rank + i] = to_f32(qr[i]);
+  }
+  float m = live ? sink[h] : 0.f, l = 1.f;
+  float acc[NR];
+#pragma unroll
+  for (int r = 0; r < NR; ++r) acc[r] = 0.f;
+
+  for (int c0 = 0; c0 <= pos; c0 += 32) {
+    const int n_keys = min(32, pos - c0 + 1);
+    __syncthreads();                                  // the chunk before is used up (and q_s is written)
+    if (threadIdx.x < 32) {
+      long long off = -1;
+      if (threadIdx.x < n_keys) {
+        const int j = c0 + threadIdx.x;
+        const int lp = j / page_size;
+        const int page = lp < max_pages ? table[lp] : -1;
+        if (page < 0 || page >= num_pages) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+        else off = ((long long)page * page_size + (j % page_size)) * Dc;
+      }
+      row_of[threadIdx.x] = off;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_keys * words; idx += blockDim.x) {
+      const int j = idx / words, w = idx - j * words;
+      const long long off = row_of[j];
+      k_s[j * stride + w] = off >= 0 ? reinterpret_cast<const unsigned*>(pages + off)[w] : 0u;
+    }
+    __syncthreads();
+    if (!live) continue;
+    const float* q = q_s + warp * Dc;
+    float s = -CUDART_INF_F;
+    if (lane < n_keys && row_of[lane] >= 0) {
+      const unsigned* kr = k_s + lane * stride;
+      float dot = 0.f;
+      for (int w = 0; w < words; ++w) dot += Word<T>::dot(q + w * EW, kr[w]);
+      s = dot * scale;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);
+    const float p = s == -CUDART_INF_F ? 0.f : expf(s - m_new);
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int r = 0; r < NR; ++r) acc[r] *= corr;
+    const T* kt = reinterpret_cast<const T*>(k_s);
+    for (int j = 0; j < n_keys; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+      const T* vr = kt + (size_t)j * stride * EW;
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        const int i = r * 32 + lane;
+        if (i < rank) acc[r] = fmaf(pj, to_f32(vr[i]), acc[r]);
+      }
+    }
+    m = m_new;
+  }
+  if (!live) return;
+  T* o = out + (size_t)t * ld_out + (size_t)h * hs_out;
+#pragma unroll
+  for (int r = 0; r < NR; ++r) {
+    const int i = r * 32 + lane;
+    if (i < rank) o[i] = from_f32<T>(acc[r] / l);
+  }
+}
+
+template <typename T, int NR>
+static int launch_latent(const void* q_abs, int ld_qa, int hs_qa, const void* q_raw, int ld_q, int hs_q,
+                         const float* cos_t, const float* sin_t, int table_len, int rdims, const void* pages,
+                         const int* block_table, int max_pages, int page_size, int num_pages, const int* positions,
+                         const int* token_req, const float* sink, float scale, void* out, int ld_out, int hs_out,
+                         int T_, int H, int rank, int rot, int* status, cudaStream_t stream) {
+  const int Dc = rank + rot;
+  const int words = Dc / Word<T>::N;
+  const size_t smem = ((size_t)kLatWarps * Dc + 32 * (size_t)(words | 1)) * 4;
+  if (smem > 200 * 1024) return KVB_ERR_BAD_SIZE;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_kernel<T, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  kvb_launch(latent_attention_kernel<T, NR>, dim3(T_, (H + kLatWarps - 1) / kLatWarps), dim3(kLatWarps * 32), smem,
+             stream, (const T*)q_abs, ld_qa, hs_qa, (const T*)q_raw, ld_q, hs_q, cos_t, sin_t, table_len, rdims,
+             (const T*)pages, block_table, max_pages, page_size, num_pages, positions, token_req, sink, scale, (T*)out,
+             ld_out, hs_out, H, rank, rot, status);
+  return kvb_launch_result();
+}
+
+// Refuses: rank > 512; in bfloat16 an odd rank + rot or a cache that is not 4-byte aligned.
+KVB_EXPORT int kvb_latent_attention(const void* q_abs, int ld_qa, int hs_qa, const void* q_raw, int ld_q, int hs_q,
+                                    const float* cos_t, const float* sin_t, int table_len, int rdims,
+                                    const void* pages, const int* block_table, int max_pages, int page_size,
+                                    int num_pages, const int* positions, const int* token_req, const float* sink,
+                                    float scale, void* out, int ld_out, int hs_out, int T_, int H, int rank, int rot,
+                                    int dtype, int* status, cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (rank < 1 || rank > 512 || rot < 0 || H < 1 || (rdims & 1) || rdims > rot) return KVB_ERR_BAD_SIZE;
+  if (dtype == KVB_BF16 && ((rank + rot) & 1)) return KVB_ERR_BAD_SIZE;
+  if (reinterpret_cast<uintptr_t>(pages) & 3) return KVB_ERR_ALIGN;
+#define KVB_LATENT(NR)                                                                                              \
+  KVB_DISPATCH_DTYPE(dtype, T, return (launch_latent<T, NR>(q_abs, ld_qa, hs_qa, q_raw, ld_q, hs_q, cos_t, sin_t,  \
+                                                            table_len, rdims, pages, block_table, max_pages,       \
+                                                            page_size, num_pages, positions, token_req, sink,      \
+                                                            scale, out, ld_out, hs_out, T_, H, rank, rot, status,  \
+                                                            stream)))
+  if (rank <= 64) { KVB_LATENT(2); }
+  else if (rank <= 128) { KVB_LATENT(4); }
+  else if (rank <= 256) { KVB_LATENT(8); }
+  else { KVB_LATENT(16); }
+#undef KVB_LATENT
+  return KVB_ERR_BAD_DTYPE;
+}

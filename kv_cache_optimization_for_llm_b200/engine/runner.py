@@ -61,6 +61,9 @@ class ModelRunner:
         config_dict = read_config_json(self.model_dir) if self.model_dir is not None else dict(random_init["config"])
         self.arch = resolve_architecture(config_dict)
         self.model_config = self.arch.parse_config(config_dict)
+        if self.arch.complete is not None and self.model_dir is not None:
+            from ..weights.loader import stored_shapes
+            self.model_config = self.arch.complete(self.model_config, stored_shapes(self.model_dir))
         self.spec = self.arch.build_spec(self.model_config)
         self.dtype = _TORCH_DTYPE[self.config.dtype]
         # Compile, side by side, what this model needs and nothing else.
@@ -92,7 +95,9 @@ class ModelRunner:
             per_token = PagedCache.bytes_per_token(specs, cache_of, self.dtype)
             free, _total = torch.cuda.mem_get_info(self.device)
             if per_token == 0:
-                num_pages = self.config.max_num_seqs
+                # nothing is kept per token (every mixer has a state of fixed size): pages cost no
+                # memory and only count tokens, so every seat gets its full length
+                num_pages = self.config.max_num_seqs * (-(-self.max_model_len // self.config.page_size))
             else:
                 num_pages = int(free * self.config.memory_fraction) // (per_token * self.config.page_size)
                 # More pages than every seat at full length can use are of no use.

@@ -235,6 +235,221 @@ def rope_kv_write(qkv, positions, token_req, cos, sin, k_pages, v_pages, block_t
     _check(rc, "rope_kv_write")
 
 
+# ------------------------------------------------------------------ norms around a branch, gated activations
+
+NORM_KINDS = {None: 0, "none": 0, "layer": 1, "rms": 2}
+
+
+class PostNormed:
+    """A branch's output that still has to pass a norm of its own before it joins the residual
+    stream: ``delta`` [T, H] (plus ``bias`` [H], float32, if the branch's last product has one),
+    the norm's ``kind`` ("layer" or "rms"), its float32 ``weight`` (a per-channel scale of the
+    branch is multiplied into it) and ``eps``.  The norm that follows (:func:`add_norm`) carries
+    it out in the kernel that also adds the result to the residual; ``materialize`` does it alone."""
+    __slots__ = ("delta", "bias", "kind", "weight", "eps")
+
+    def __init__(self, delta, bias, kind, weight, eps):
+        self.delta, self.bias, self.kind, self.weight, self.eps = delta, bias, kind, weight, float(eps)
+
+    def materialize(self) -> torch.Tensor:
+        """The normed branch output as a tensor of its own, for a norm that cannot take it in."""
+        zero = torch.zeros(self.delta.shape, dtype=torch.float32, device=self.delta.device)
+        add_norm(zero, self, None, None, 0.0, self.delta.dtype)
+        return zero.to(self.delta.dtype)
+
+
+def add_norm(resid: torch.Tensor, pending, kind: Optional[str], weight: Optional[torch.Tensor], eps: float,
+             out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``resid += post(pending)`` in float32 (in place unless ``rows`` selects), then the norm
+    ``kind`` ("layer": (v - mean) / sqrt(var + eps), "rms": v / sqrt(mean(v^2) + eps)) of the sum
+    times ``weight``.  ``pending``: None, a tensor [T, H] that is added as it is, or a
+    :class:`PostNormed`.  ``kind`` None: only the residual is brought up to date."""
+    _need_cuda(resid)
+    assert resid.dtype == torch.float32 and resid.is_contiguous()
+    T, H = resid.shape
+    delta = bias = post_w = None
+    post_kind, post_eps = 0, 0.0
+    if isinstance(pending, PostNormed):
+        delta, bias, post_w = pending.delta, pending.bias, pending.weight
+        post_kind, post_eps = NORM_KINDS[pending.kind], pending.eps
+    elif pending is not None:
+        delta = pending
+    if delta is not None:
+        assert delta.shape == resid.shape and delta.is_contiguous() and delta.dtype in (torch.float32, torch.bfloat16)
+        assert delta.dtype == out_dtype
+    n = T if rows is None else rows.numel()
+    out = new((n, H), out_dtype, resid.device) if kind is not None else None
+    rc = lib("rowwise").kvb_add_norm(_p(resid), _p(delta), _p(bias), _p(post_w), c_int(post_kind), c_float(post_eps),
+                                     _p(weight), c_int(NORM_KINDS[kind]), c_float(eps), _p(out), _p(rows), c_int(n),
+                                     c_int(H), c_int(dtype_code(out_dtype)), _stream())
+    _check(rc, "add_norm")
+    return out
+
+
+ACT_KINDS = {"silu": 0, "gelu_tanh": 1}
+
+
+def bias_act_mul(gate_up: torch.Tensor, bias: Optional[torch.Tensor], act: str) -> torch.Tensor:
+    """``act(gate + b_gate) * (up + b_up)`` for rows that hold [gate | up]; ``bias`` float32 [2 I] or None."""
+    _need_cuda(gate_up)
+    assert gate_up.is_contiguous() and (bias is None or (bias.dtype == torch.float32 and bias.numel() == gate_up.shape[1]))
+    T, two_i = gate_up.shape
+    out = new((T, two_i // 2), gate_up.dtype, gate_up.device)
+    rc = lib("rowwise").kvb_bias_act_mul(_p(gate_up), _p(bias), _p(out), c_int(T), c_int(two_i // 2),
+                                         c_int(ACT_KINDS[act]), c_int(dtype_code(gate_up.dtype)), _stream())
+    _check(rc, "bias_act_mul")
+    return out
+
+
+def tanh_slice(x: torch.Tensor, first: int, n: int) -> torch.Tensor:
+    """``tanh(x[:, first:first + n])`` as a dense tensor."""
+    _need_cuda(x)
+    assert x.stride(1) == 1
+    out = new((x.shape[0], n), x.dtype, x.device)
+    rc = lib("rowwise").kvb_tanh_slice(c_void_p(x.data_ptr() + first * x.element_size()), c_int(x.stride(0)), _p(out),
+                                       c_int(x.shape[0]), c_int(n), c_int(dtype_code(x.dtype)), _stream())
+    _check(rc, "tanh_slice")
+    return out
+
+
+# ------------------------------------------------------------------ mixers with a matrix state (delta-rule family)
+
+class _DeltaArgs(ctypes.Structure):
+    _fields_ = [("r", c_void_p), ("ld_r", c_int), ("k", c_void_p), ("ld_k", c_int), ("v", c_void_p), ("ld_v", c_int),
+                ("gate", c_void_p), ("ld_gate", c_int), ("decay", c_void_p), ("ld_decay", c_int),
+                ("aux", c_void_p), ("ld_aux", c_int), ("decay_bias", c_void_p), ("aux_bias", c_void_p),
+                ("head_rate", c_void_p), ("norm_w", c_void_p), ("norm_per_head", c_int), ("state", c_void_p),
+                ("slot_stride", c_longlong), ("out", c_void_p), ("ld_out", c_int), ("q_start", c_void_p),
+                ("req_start", c_void_p), ("slots", c_void_p), ("H", c_int), ("G", c_int), ("Dk", c_int), ("Dv", c_int),
+                ("eps", c_float)]
+
+
+_key_pad: Dict[int, int] = {}
+
+
+def delta_key_pad(dk: int) -> int:
+    """Floats per column of a head's state for key size ``dk`` (the kernel pads it), 0 if refused."""
+    if dk not in _key_pad:
+        _key_pad[dk] = int(lib("delta_rule").kvb_delta_key_pad(c_int(int(dk))))
+    return _key_pad[dk]
+
+
+def _at(t: torch.Tensor, col: int) -> int:
+    return t.data_ptr() + col * t.element_size()
+
+
+def delta_scan(mode: str, batch, state: torch.Tensor, r, k, v, gate, decay, aux, decay_bias, aux_bias, head_rate,
+               norm_w, norm_per_head: bool, heads: int, key_heads: int, dk: int, dv: int, eps: float) -> torch.Tensor:
+    """One step of a delta-rule mixer for every request of the batch: walks each request's new
+    tokens in order from the state in its slot (zero for a request that starts at position 0)
+    and leaves the new state there.  ``r, k, v, gate, decay, aux``: (tensor, first column) pairs
+    naming where each projection lies in a [T, *] tensor of the compute type.  ``state``:
+    float32 [slots, >= heads * dv * delta_key_pad(dk)], a request's slot row starting with the
+    matrix states.  ``mode``: "general" or "gated" (see csrc/kernels/delta_rule.cu).
+    Returns the gated, normed read-out [T, heads * dv]."""
+    x0 = r[0]
+    _need_cuda(x0, state)
+    T = x0.shape[0]
+    assert state.dtype == torch.float32 and state.stride(-1) == 1
+    out = new((T, heads * dv), x0.dtype, x0.device)
+    a = _DeltaArgs()
+    for name, (t, col) in (("r", r), ("k", k), ("v", v), ("gate", gate), ("decay", decay), ("aux", aux)):
+        assert t.dtype == x0.dtype and t.stride(1) == 1 and t.shape[0] == T
+        setattr(a, name, _at(t, col))
+        setattr(a, "ld_" + name, t.stride(0))
+    for name, t in (("decay_bias", decay_bias), ("aux_bias", aux_bias), ("head_rate", head_rate), ("norm_w", norm_w)):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+        setattr(a, name, 0 if t is None else t.data_ptr())
+    a.norm_per_head = 1 if norm_per_head else 0
+    a.state, a.slot_stride = state.data_ptr(), state.stride(0)
+    a.out, a.ld_out = out.data_ptr(), out.stride(0)
+    a.q_start, a.req_start, a.slots = batch.q_start.data_ptr(), batch.req_start.data_ptr(), batch.slots.data_ptr()
+    a.H, a.G, a.Dk, a.Dv, a.eps = heads, key_heads, dk, dv, eps
+    rc = lib("delta_rule").kvb_delta_scan(ctypes.byref(a), c_int({"general": 0, "gated": 1}[mode]),
+                                          c_int(batch.num_reqs), c_int(dtype_code(x0.dtype)), _stream())
+    _check(rc, "delta_scan")
+    choices["delta_scan_" + mode] += 1
+    return out
+
+
+def conv_silu(x: torch.Tensor, first: int, channels: int, w: torch.Tensor, tails: Optional[torch.Tensor],
+              batch) -> torch.Tensor:
+    """``silu`` of a short causal convolution over time per channel of ``x[:, first:first + channels]``.
+    ``w`` float32 [channels, taps], last column for the token itself.  ``tails``: float32
+    [slots, >= (taps - 1) * channels], a view whose row r starts with request slot r's last
+    ``taps - 1`` inputs; it is read for the inputs in front of the step's tokens and brought up to date."""
+    _need_cuda(x, w)
+    taps = w.shape[1]
+    assert w.dtype == torch.float32 and w.is_contiguous() and x.stride(1) == 1
+    assert taps == 1 or (tails is not None and tails.dtype == torch.float32 and tails.stride(-1) == 1)
+    out = new((x.shape[0], channels), x.dtype, x.device)
+    rc = lib("delta_rule").kvb_conv_silu(
+        c_void_p(_at(x, first)), c_int(x.stride(0)), _p(w), c_int(taps), _p(tails),
+        c_longlong(0 if tails is None else tails.stride(0)), _p(out), c_int(channels), c_int(x.shape[0]),
+        c_int(batch.num_reqs), _p(batch.positions), _p(batch.token_req), _p(batch.q_start), _p(batch.req_start),
+        _p(batch.ctx_len), _p(batch.slots), c_int(dtype_code(x.dtype)), _stream())
+    _check(rc, "conv_silu")
+    global launch_count
+    launch_count += 1 if taps > 1 else 0   # the convolution and the tails' update
+    return out
+
+
+# ------------------------------------------------------------------ attention over a cached latent
+
+def latent_prep(d_in: torch.Tensor, q_rank: int, kv_off: int, rank: int, rot: int, rdims: int, wq, wkv, eps: float,
+                cos, sin, batch, block_table, pages: torch.Tensor, write: bool) -> torch.Tensor:
+    """RMS norm of the query latent (returned, [T, q_rank]); RMS norm of the key/value latent and
+    interleaved rotary encoding of the shared key part, both written to the token's cache row."""
+    _need_cuda(d_in, pages)
+    assert d_in.stride(1) == 1 and pages.is_contiguous() and pages.dtype == d_in.dtype
+    assert pages.shape[1] == 1 and pages.shape[3] == rank + rot
+    T = d_in.shape[0]
+    cq = new((T, q_rank), d_in.dtype, d_in.device)
+    rc = lib("latent_attention").kvb_latent_prep(
+        _p(d_in), c_int(d_in.stride(0)), c_int(q_rank), c_int(kv_off), c_int(rank), c_int(rot), c_int(rdims), _p(wq),
+        _p(wkv), c_float(eps), _p(cos), _p(sin), c_int(0 if cos is None else cos.shape[0]), _p(batch.positions),
+        _p(batch.token_req), _p(block_table), c_int(block_table.shape[1]), c_int(pages.shape[2]), c_int(pages.shape[0]),
+        _p(cq), _p(pages), c_int(1 if write else 0), c_int(T), c_int(dtype_code(d_in.dtype)), _p(batch.status), _stream())
+    _check(rc, "latent_prep")
+    return cq
+
+
+def head_gemm(x: torch.Tensor, first: int, head_stride: int, w: torch.Tensor) -> torch.Tensor:
+    """A product per head: ``out[t, h, :] = w[h] @ x[t, first + h * head_stride : ... + K]`` with
+    ``w`` [H, N, K]; float32 sums in ascending k.  Returns [T, H * N]."""
+    _need_cuda(x, w)
+    H, N, K = w.shape
+    assert w.is_contiguous() and w.dtype == x.dtype and x.stride(1) == 1
+    out = new((x.shape[0], H * N), x.dtype, x.device)
+    rc = lib("latent_attention").kvb_head_gemm(c_void_p(_at(x, first)), c_int(x.stride(0)), c_int(head_stride), _p(w),
+                                               _p(out), c_int(out.stride(0)), c_int(N), c_int(x.shape[0]), c_int(N),
+                                               c_int(K), c_int(H), c_int(dtype_code(x.dtype)), _stream())
+    _check(rc, "head_gemm")
+    return out
+
+
+def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, rot_first: int, q_head_stride: int, cos, sin, rdims: int,
+                     pages: torch.Tensor, block_table, batch, sink: torch.Tensor, scale: float, heads: int,
+                     rank: int, rot: int) -> torch.Tensor:
+    """Causal attention of every token over its request's cached rows [latent | rotated part],
+    all heads sharing the rows; softmax with a sink per head.  ``q_abs`` [T, heads * rank]: the
+    queries' plain parts moved into the latent's space; ``q`` holds head h's part to be rotated at
+    ``rot_first + h * q_head_stride``.  Returns the attended latents [T, heads * rank]."""
+    _need_cuda(q_abs, pages)
+    assert q_abs.is_contiguous() and q.stride(1) == 1 and pages.is_contiguous() and sink.dtype == torch.float32
+    T = q_abs.shape[0]
+    out = new((T, heads * rank), q_abs.dtype, q_abs.device)
+    rc = lib("latent_attention").kvb_latent_attention(
+        _p(q_abs), c_int(q_abs.stride(0)), c_int(rank), c_void_p(_at(q, rot_first)), c_int(q.stride(0)),
+        c_int(q_head_stride), _p(cos), _p(sin), c_int(0 if cos is None else cos.shape[0]), c_int(rdims), _p(pages),
+        _p(block_table), c_int(block_table.shape[1]), c_int(pages.shape[2]), c_int(pages.shape[0]), _p(batch.positions),
+        _p(batch.token_req), _p(sink), c_float(scale), _p(out), c_int(out.stride(0)), c_int(rank), c_int(T),
+        c_int(heads), c_int(rank), c_int(rot), c_int(dtype_code(q_abs.dtype)), _p(batch.status), _stream())
+    _check(rc, "latent_attention")
+    choices["latent_attention"] += 1
+    return out
+
+
 # ------------------------------------------------------------------ attention
 
 def paged_attention_generic(qkv, k_pages, v_pages, block_table, positions, token_req, nq, nkv, d,

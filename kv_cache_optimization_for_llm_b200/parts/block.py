@@ -51,3 +51,44 @@ class PreNormBlock(Part):
         else:
             f = self.feed_forward.forward(self.ff_norm.forward(residual, a), batch)
         return residual, f
+
+
+@register("block", "sandwich")
+class SandwichBlock(Part):
+    """``h += post1(mixer(pre1(h))); h += post2(ff(pre2(h)))``: a norm in front of each sublayer and
+    one behind it, before the residual add.  A per-channel scale of a branch belongs to its post
+    norm (``scaled``).  The post norm is not a launch of its own: the branch output travels on as
+    an :class:`ops.PostNormed`, and the next pre norm (of this layer, of the next one, or the
+    model's last norm) norms it, adds it and norms the sum in one kernel.  A feed-forward that
+    ends in a bias hands it over with its output (``forward(..., bias_out=True)``)."""
+
+    part_families = {"mixer": "mixer", "mixer_norm": "norm", "mixer_post_norm": "norm",
+                     "feed_forward": "feed_forward", "ff_norm": "norm", "ff_post_norm": "norm"}
+
+    def __init__(self, parts):
+        self.parts = dict(parts)
+        self.mixer, self.mixer_norm, self.mixer_post = parts["mixer"], parts["mixer_norm"], parts["mixer_post_norm"]
+        self.feed_forward = parts.get("feed_forward")
+        self.ff_norm, self.ff_post = parts.get("ff_norm"), parts.get("ff_post_norm")
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, residual, delta, batch, cache):
+        a = self.mixer.forward(self.mixer_norm.forward(residual, delta), batch, cache)
+        pending = self.mixer_post.as_pending(a)
+        if self.feed_forward is None:
+            return residual, pending
+        x = self.ff_norm.forward(residual, pending)
+        if getattr(self.feed_forward, "hands_over_bias", False):
+            f, bias = self.feed_forward.forward(x, batch, bias_out=True)
+        else:
+            f, bias = self.feed_forward.forward(x, batch), None
+        return residual, self.ff_post.as_pending(f, bias)
+
+
+@register("block", "sandwich_mixer_only")
+class SandwichMixerBlock(SandwichBlock):
+    """The sandwich block of a layer that has no feed-forward: ``h += post1(mixer(pre1(h)))``."""
+
+    part_families = {"mixer": "mixer", "mixer_norm": "norm", "mixer_post_norm": "norm"}

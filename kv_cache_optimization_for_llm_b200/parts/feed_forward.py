@@ -57,3 +57,52 @@ class SwiGLU(Part):
     def forward(self, x, batch, into=None):
         a = ops.linear_swiglu(x, self.gate_up, self.block)
         return ops.linear(a, self.down, into=into)
+
+
+@register("feed_forward", "gated_dense")
+class GatedDense(Part):
+    """``down( act(gate(x) + b_gate) * (up(x) + b_up) ) + b_down`` with ``act`` the tanh form of GELU
+    (or SiLU).  gate and up are one [2 I, H] matrix; their biases and the activation are one kernel
+    behind the product.  The last bias can be handed to the caller instead of being added here
+    (``bias_out``), for a norm kernel that adds it while it reads the rows anyway.
+    params: hidden_size, intermediate_size, activation ("gelu_tanh" or "silu"), bias (bool)."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        h, i = params["hidden_size"], params["intermediate_size"]
+        specs = {"gate": WeightSpec((i, h)), "up": WeightSpec((i, h)), "down": WeightSpec((h, i))}
+        if params.get("bias", True):
+            specs.update(gate_bias=WeightSpec((i,), "bias"), up_bias=WeightSpec((i,), "bias"),
+                         down_bias=WeightSpec((h,), "bias"))
+        return specs
+
+    @classmethod
+    def kernel_modules(cls, params, dtype):
+        return ("rowwise",) + (("gemm_f32",) if dtype == torch.float32 else ("gemm_bf16", "gemm_bf16_wide"))
+
+    hands_over_bias = True
+
+    def __init__(self, params, weights, ctx):
+        super().__init__(params, weights, ctx)
+        self.act = str(params.get("activation", "gelu_tanh"))
+        if self.act not in ops.ACT_KINDS:
+            raise ValueError(f"activation {self.act!r} is not known to this feed-forward (known: {sorted(ops.ACT_KINDS)})")
+        self.gate_up = torch.cat([weights["gate"], weights["up"]], dim=0).contiguous()
+        self.down = weights["down"]
+        self.bias = self.down_bias = None
+        if params.get("bias", True):
+            self.bias = torch.cat([weights["gate_bias"], weights["up_bias"]]).contiguous()
+            self.down_bias = weights["down_bias"]
+
+    def activation_widths(self):
+        inter, hidden = self.gate_up.shape[0] // 2, self.down.shape[0]
+        return [2 * inter, inter, hidden]
+
+    def forward(self, x, batch, bias_out=False):
+        a = ops.bias_act_mul(ops.linear(x, self.gate_up), self.bias, self.act)
+        y = ops.linear(a, self.down)
+        if bias_out:
+            return y, self.down_bias
+        if self.down_bias is not None:
+            y = y + self.down_bias.to(y.dtype)
+        return y

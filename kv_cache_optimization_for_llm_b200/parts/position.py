@@ -59,3 +59,27 @@ class RotaryEncoding(Part):
 
     def tables(self):
         return self.cos, self.sin
+
+
+@register("position", "rope_interleaved")
+class InterleavedRotaryEncoding(Part):
+    """Rotary encoding whose pairs are neighbours: dimension 2i turns with dimension 2i + 1 by
+    the angle ``pos * base^(-2i/dims)`` for i < dims/2; dimensions from ``dims`` on pass unchanged.
+    Holds float32 tables ``cos, sin [max_positions, dims/2]`` with angles formed in float64; the
+    rotation itself runs inside the mixer's kernels.  params: dims, base."""
+
+    def __init__(self, params, weights, ctx):
+        super().__init__(params, weights, ctx)
+        self.rotary_dim = int(params["dims"])
+        if self.rotary_dim % 2 or self.rotary_dim < 0:
+            raise ValueError(f"rotary dims {self.rotary_dim} must be even")
+        key = ("rope_interleaved", self.rotary_dim, float(params["base"]), ctx.max_positions)
+        if key not in ctx.shared:
+            inv = rope_inv_freq(self.rotary_dim, float(params["base"]), None) if self.rotary_dim else torch.zeros(0, dtype=torch.float64)
+            ang = torch.arange(ctx.max_positions, dtype=torch.float64)[:, None] * inv[None, :]
+            ctx.shared[key] = (ang.cos().to(torch.float32).to(ctx.device).contiguous(),
+                               ang.sin().to(torch.float32).to(ctx.device).contiguous())
+        self.cos, self.sin = ctx.shared[key]
+
+    def tables(self):
+        return self.cos, self.sin

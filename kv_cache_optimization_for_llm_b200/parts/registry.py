@@ -35,4 +35,4 @@ def known(family: str):
 
 
 def _load_builtin() -> None:
-    from . import attention, block, embedding, feed_forward, norm, position  # noqa: F401
+    from . import attention, block, delta_rule, embedding, feed_forward, latent_attention, norm, position  # noqa: F401

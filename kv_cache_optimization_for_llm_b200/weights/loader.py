@@ -21,7 +21,8 @@ from .safetensors_io import SafetensorsError, read_header, read_tensors
 @dataclass(frozen=True)
 class WeightSpec:
     """What a part expects of one tensor.  ``kind``: 'matrix' (cast to the compute
-    dtype), 'vector' (kept in 32-bit: norm weights) or 'table' (integers, int32)."""
+    dtype), 'vector' (kept in 32-bit: norm weights), 'bias' (kept in 32-bit, centred on zero:
+    biases and other small vectors that enter 32-bit arithmetic) or 'table' (integers, int32)."""
     shape: Tuple[int, ...]
     kind: str = "matrix"
 
@@ -59,6 +60,16 @@ def _files(model_dir: Path):
     raise FileNotFoundError(f"{model_dir} holds neither model.safetensors nor model.safetensors.index.json")
 
 
+def stored_shapes(model_dir) -> Dict[str, Tuple[int, ...]]:
+    """name -> shape of every tensor in the folder's checkpoint, from the headers alone."""
+    out: Dict[str, Tuple[int, ...]] = {}
+    for f in _files(Path(model_dir)):
+        header, _ = read_header(f)
+        for name, meta in header.items():
+            out[name] = tuple(int(n) for n in meta["shape"])
+    return out
+
+
 def check_and_load(model_dir, expected: Mapping[str, WeightSpec]) -> Dict[str, torch.Tensor]:
     """Returns name -> CPU tensor in the stored dtype for exactly the expected names."""
     model_dir = Path(model_dir)
@@ -94,6 +105,6 @@ def to_compute(t: torch.Tensor, spec: WeightSpec, dtype: torch.dtype, device) ->
     the 32-bit path); vectors are kept in 32-bit; integer tables become int32."""
     if spec.kind == "table":
         return t.to(device=device, dtype=torch.int32).contiguous()
-    if spec.kind == "vector":
+    if spec.kind in ("vector", "bias"):
         return t.to(device=device, dtype=torch.float32).contiguous()
     return t.to(device=device, dtype=dtype).contiguous()

@@ -48,7 +48,7 @@ def random_tensors_on_device(expected: Mapping[str, WeightSpec], seed: int, std:
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
             continue
         t = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device) * std
-        out[name] = (t + 1.0) if spec.kind == "vector" else t.to(dtype)
+        out[name] = (t + 1.0) if spec.kind == "vector" else (t if spec.kind == "bias" else t.to(dtype))
     return out
 
 
