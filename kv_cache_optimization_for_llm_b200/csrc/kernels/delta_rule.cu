@@ -157,8 +157,9 @@ __global__ void delta_scan_kernel(const DeltaArgs a) {
       smem[(size_t)c * tok_floats + 5 * DKP + j] = cv;
     }
     __syncthreads();
-    // ---- the scan over the chunk
-    if (col < dvp) {
+    // ---- the scan over the chunk.  Every thread takes part (the shuffles name the whole warp);
+    // threads beyond the last column carry zeros and store nothing.
+    {
       for (int c = 0; c < n; ++c) {
         const float* tok = smem + (size_t)c * tok_floats;
         const float4* D4 = reinterpret_cast<const float4*>(tok);
@@ -177,9 +178,9 @@ __global__ void delta_scan_kernel(const DeltaArgs a) {
         }
         dx += __shfl_xor_sync(0xffffffffu, dx, 1); dy += __shfl_xor_sync(0xffffffffu, dy, 1);
         dx += __shfl_xor_sync(0xffffffffu, dx, 2); dy += __shfl_xor_sync(0xffffffffu, dy, 2);
-        const float cj = tok[5 * DKP + col];
+        const float cj = col < dvp ? tok[5 * DKP + col] : 0.f;
         const float pr = tok[5 * DKP + 2 * dvp], kr = tok[5 * DKP + 2 * dvp + 1];
-        if (part == 0) smem[(size_t)c * tok_floats + 5 * DKP + dvp + col] = dy - dx * pr + cj * kr;
+        if (part == 0 && col < dvp) smem[(size_t)c * tok_floats + 5 * DKP + dvp + col] = dy - dx * pr + cj * kr;
 #pragma unroll
         for (int e4 = 0; e4 < KPL / 4; ++e4) {
           const float4 dv = D4[e4 * 4 + part], pv = P4[e4 * 4 + part], kv = K4[e4 * 4 + part];

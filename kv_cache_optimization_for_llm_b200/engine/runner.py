@@ -299,6 +299,7 @@ class ModelRunner:
         # one graph per padded batch size and class of context length (launches are sized by both)
         key = (bucket, ops.decode_context_class(batch.max_ctx_len))
         got = self._graphs.get(key)
+        captured_now = got is None
         if got is None:
             # Every row's logits are produced; rows are picked after the replay.
             rows = torch.arange(bucket, dtype=torch.int32, device=self.device)
@@ -328,8 +329,15 @@ class ModelRunner:
             self._graphs[key] = got
             ops.launch_count = before                       # captured, not launched
         graph, out, launches, _rows = got
-        graph.replay()
-        self.graph_launches += launches
+        if captured_now and self.cache.states:
+            # The warm-up in front of the capture has already run this very step, and ``out`` (a tensor
+            # of the arena, at the same place for every step of this shape) holds its logits.  A mixer
+            # with a state of fixed size must not see the step's tokens twice; keys and values written
+            # twice to the same place do no harm, so models without such mixers replay as before.
+            pass
+        else:
+            graph.replay()
+            self.graph_launches += launches
         if all(wants):
             return out[:n]
         keep = [i for i, w in enumerate(wants) if w]

@@ -55,7 +55,7 @@ def test_config_errors_name_the_key(patch, word):
 
 
 def test_registry_knows_llama_and_rejects_others():
-    assert known_architectures() == ["LlamaForCausalLM"]
+    assert "LlamaForCausalLM" in known_architectures()
     arch = resolve_architecture(TINY_A)
     spec = arch.build_spec(arch.parse_config(TINY_A))
     assert len(spec.layers) == 2 and [e.layer for e in spec.schedule] == [0, 1]
