@@ -395,6 +395,159 @@ def run_workload(name, seed=0):
     return res
 
 
+# ---------------------------------------------------------------------------------------------
+# Two designs at equal size (bench.py --compare <size>)
+# ---------------------------------------------------------------------------------------------
+COMPARE_SIZES = {
+    # width, feed-forward, vocabulary, layers; heads of 64 for Llama and the delta-rule mixers; the latent attention
+    # with heads of dim + rot and a latent of four value heads' width
+    "w1024": dict(width=1024, ff=4096, vocab=32768, layers=6, heads=16, lat_heads=8, lat_dim=64, lat_rot=32, lat_vdim=64,
+                  q_rank=384, kv_rank=256, low_rank=64),
+    "w2048": dict(width=2048, ff=8192, vocab=32768, layers=6, heads=32, lat_heads=16, lat_dim=128, lat_rot=64,
+                  lat_vdim=128, q_rank=768, kv_rank=512, low_rank=64),
+}
+FP32_FMA_TFLOPS_NOMINAL = 75.0    # 148 SMs x 128 lanes x 2 x ~1.97 GHz: no measured figure for the CUDA cores is at hand
+
+
+def rezusun_config(z):
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    general = {"type": "general_delta", "mixer": {"heads": z["heads"], "dim": 64, "decay_rank": z["low_rank"]}, "mlp": mlp}
+    channel = {"type": "channel_delta", "mixer": {"heads": z["heads"], "kv_heads": z["heads"] // 4, "dim": 64, "vdim": 64,
+                                                 "conv": 4, "decay_rank": z["low_rank"], "gate_rank": z["low_rank"]}, "mlp": mlp}
+    latent = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": z["lat_heads"], "dim": z["lat_dim"], "rot_dim": z["lat_rot"], "vdim": z["lat_vdim"], "q_rank": z["q_rank"],
+        "kv_rank": z["kv_rank"], "scale": (z["lat_dim"] + z["lat_rot"]) ** -0.5, "rot": {"base": 10000.0, "dims": z["lat_rot"]}}}
+    return {"architecture": "Rezusun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "layers": [[general, channel, latent][i % 3] for i in range(z["layers"])], "loop": None,
+            "max_position_embeddings": CONTEXT_LEN}
+
+
+def llama_config_like(z):
+    cfg = dict(LLAMA_1B)
+    cfg.update(hidden_size=z["width"], intermediate_size=z["ff"], vocab_size=z["vocab"], num_hidden_layers=z["layers"],
+               num_attention_heads=z["heads"], num_key_value_heads=z["heads"] // 4, head_dim=64,
+               tie_word_embeddings=False, max_position_embeddings=CONTEXT_LEN)
+    return cfg
+
+
+def _time_steps(fn, reps, warmup):
+    import torch
+    times = []
+    for k in range(warmup + reps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        fn(k)
+        stop.record()
+        torch.cuda.synchronize()
+        if k >= warmup:
+            times.append(start.elapsed_time(stop))
+    return statistics.median(times)
+
+
+def measure_design(config_dict, decode_batch=8, decode_batch_ops=64):
+    """Prefill of one 2048-token portion and decode steps (from CUDA graphs) of a random model through the
+    step function; then one launched step of each kind with an event behind every operator."""
+    import numpy as np
+    import torch
+    from kv_cache_optimization_for_llm_b200 import EngineConfig, ops
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
+    seats = decode_batch_ops
+    r = ModelRunner(None, EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_num_seqs=seats,
+                                       num_pages=seats * (PROMPT_LEN + 64) // PAGE_SIZE + PREFILL_TOKENS // PAGE_SIZE,
+                                       max_num_batched_tokens=PREFILL_TOKENS, max_model_len=CONTEXT_LEN),
+                    random_init={"config": config_dict, "seed": 0, "std": 0.02})
+    rng = np.random.default_rng(0)
+    toks = rng.integers(0, r.vocab_size, PREFILL_TOKENS).tolist()
+
+    def prefill(k):
+        r.step([StepEntry(1000 + k, toks, 0, [PREFILL_TOKENS - 1])])
+        r.release(1000 + k)
+    out = {"weight_bytes": r.weight_bytes}
+    ms = _time_steps(prefill, 5, 2)
+    out["prefill_2048"] = {"ms": round(ms, 3), "tok_per_s": round(PREFILL_TOKENS / ms * 1e3)}
+    with ops.timed_operators() as t:
+        prefill(99)
+    out["prefill_2048"]["operators"] = {k: [n, round(v, 3)] for k, (n, v) in sorted(t.times.items())}
+    r.check_status()
+    for batch, timed_ops in ((decode_batch, False), (decode_batch_ops, True)):
+        prompts = [rng.integers(0, r.vocab_size, PROMPT_LEN + 48).tolist() for _ in range(batch)]
+        for i in range(0, batch, 4):
+            r.step([StepEntry(j, prompts[j][:PROMPT_LEN], 0, []) for j in range(i, min(batch, i + 4))])
+        pos = [PROMPT_LEN]
+
+        def decode(k):
+            r.step([StepEntry(j, [prompts[j][pos[0]]], pos[0], [0]) for j in range(batch)])
+            pos[0] += 1
+        ms = _time_steps(decode, 24, 4)
+        out[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4), "tok_per_s": round(batch / ms * 1e3), "context": PROMPT_LEN}
+        if timed_ops:
+            buckets, r.graph_buckets = r.graph_buckets, []      # one step launched kernel by kernel
+            decode(0)
+            with ops.timed_operators() as t:
+                decode(1)
+            r.graph_buckets = buckets
+            out[f"decode_b{batch}"]["operators_launched"] = {k: [n, round(v, 4)] for k, (n, v) in sorted(t.times.items())}
+        for j in range(batch):
+            r.release(j)
+    r.check_status()
+    del r
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_compare(size):
+    """The Rezusun design beside Llama at equal width, depth, feed-forward and vocabulary."""
+    z = COMPARE_SIZES[size]
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    w0 = time.perf_counter()
+    log(f"{size}: Llama")
+    llama = measure_design(llama_config_like(z))
+    log(f"{size}: Rezusun")
+    rez = measure_design(rezusun_config(z))
+    w1 = time.perf_counter()
+    sampler.stop()
+    T, R, ctx = PREFILL_TOKENS, 64, PROMPT_LEN
+    pairs = T * (T + 1) // 2
+    n_each = z["layers"] // 3
+    H, Dk = z["heads"], 64
+    dc = z["kv_rank"] + z["lat_rot"]
+
+    def per_launch(d, phase, key, name):
+        n, ms = d[phase][key].get(name, (0, 0.0))
+        return ms / n if n else None
+
+    def frac(work, ms, peak_per_s):
+        return None if not ms else round(work / (ms * 1e-3) / peak_per_s, 4)
+    tensor, hbm, fma = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9, FP32_FMA_TFLOPS_NOMINAL * 1e12
+    kernels = {
+        # prefill: FLOPs of the kernel's own arithmetic over the time of one launch
+        "llama flash_attention, 2048 tokens (of the measured bf16 peak)": frac(
+            pairs * 4 * z["heads"] * 64, per_launch(llama, "prefill_2048", "operators", "paged_flash_attention"), tensor),
+        "rezusun latent_attention, 2048 tokens (of the nominal fp32 FMA peak)": frac(
+            pairs * z["lat_heads"] * 2 * (dc + z["kv_rank"]), per_launch(rez, "prefill_2048", "operators", "latent_attention"), fma),
+        "rezusun delta_scan, 2048 tokens (of the nominal fp32 FMA peak)": frac(
+            T * H * Dk * 64 * 10, per_launch(rez, "prefill_2048", "operators", "delta_scan"), fma),
+        # decode, 64 requests at 512 tokens: bytes that must move over the time of one launch
+        "llama decode_attention_mma, batch 64 (of the measured copy peak)": frac(
+            R * ctx * 2 * (z["heads"] // 4) * 64 * 2, per_launch(llama, "decode_b64", "operators_launched", "decode_attention_mma"), hbm),
+        "rezusun latent_attention, batch 64 (of the measured copy peak)": frac(
+            R * ctx * dc * 2, per_launch(rez, "decode_b64", "operators_launched", "latent_attention"), hbm),
+        "rezusun delta_scan, batch 64 (of the measured copy peak)": frac(
+            2 * R * H * 64 * Dk * 4, per_launch(rez, "decode_b64", "operators_launched", "delta_scan"), hbm),
+        "llama add_rmsnorm, 2048 tokens (of the measured copy peak)": frac(
+            T * z["width"] * 12, per_launch(llama, "prefill_2048", "operators", "add_rmsnorm"), hbm),
+        "rezusun add_norm, 2048 tokens (of the measured copy peak)": frac(
+            T * z["width"] * 12, per_launch(rez, "prefill_2048", "operators", "add_norm"), hbm),
+    }
+    return {"compare": size, "sizes": z, "dtype": "bf16", "data": "synthetic", "peaks": pk, "llama": llama, "rezusun": rez,
+            "kernel_roofline_fractions": kernels, "layers_of_each_kind": n_each,
+            "clocks": sampler.summary([(w0, w1)])}
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -411,8 +564,15 @@ def main():
     ap.add_argument("--workload", default="all", choices=["all", "none", *WORKLOADS],
                     help="the serving workloads measured beside the headline (3B continuous batching, 8B under a "
                          "pool that is too small); one name runs that workload alone and prints its own JSON line")
+    ap.add_argument("--compare", default=None, choices=sorted(COMPARE_SIZES),
+                    help="instead of the headline: prefill and decode of the Rezusun design beside a Llama model of "
+                         "equal width, depth, feed-forward and vocabulary (random weights), with the time of every "
+                         "operator and roofline fractions of the designs' own kernels; prints its own JSON line")
     args = ap.parse_args()
 
+    if args.compare:
+        print(json.dumps(run_compare(args.compare)), flush=True)
+        return 0
     if args.impl == "reference":
         # upstream's own engine, unmodified, driven through its standard input and output
         sys.path.insert(0, os.path.join(ROOT, "baseline"))

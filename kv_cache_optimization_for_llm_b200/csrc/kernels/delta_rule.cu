@@ -17,9 +17,10 @@
 // token, so one round of shuffles per token serves both the update and the read-out.
 //
 // A block owns one (head, request): it walks the request's tokens of this step in chunks of
-// 16: all warps turn the chunk's projections into the float32 vectors above (one warp per
-// token), then every thread steps through the chunk, then the warps finish the chunk's
-// outputs (RMS over the head, weight, sigmoid gate).  The state is read from the request's
+// 16.  A chunk is prepared (its projections become the float32 vectors above, one warp per
+// token), scanned (the threads that own the columns step through it) and finished (RMS over
+// the head, weight, sigmoid gate); up to sixteen more warps prepare chunk i + 1 and finish
+// chunk i - 1 while the scan walks chunk i, in two buffers, one block barrier per chunk.  The state is read from the request's
 // slot at the start (zero when the request starts at position 0) and written back at the end.
 // Everything but the projections is float32.  A token's result does not depend on how the
 // request was cut into steps: each token is prepared alone and the scan is sequential.
@@ -58,7 +59,7 @@ __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 template <typename T, int KPL, int MODE>
-__global__ void delta_scan_kernel(const DeltaArgs a) {
+__global__ void delta_scan_kernel(const DeltaArgs a, int n_scan) {
   constexpr int DKP = 4 * KPL;
   extern __shared__ float4 smem4[];
   float* smem = reinterpret_cast<float*>(smem4);
@@ -68,8 +69,14 @@ __global__ void delta_scan_kernel(const DeltaArgs a) {
   const int Dk = a.Dk, Dv = a.Dv;
   const int dvp = (Dv + 3) & ~3;
   const int tok_floats = 5 * DKP + 2 * dvp + 4;      // d, p, x, k, y | c | o | (p.r, k.r)
+  const int buf_floats = kChunk * tok_floats;
   const int t0 = a.q_start[req], t1 = a.q_start[req + 1];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // The first n_scan threads own the columns; the others (if the block has any) prepare the
+  // next chunk and finish the one before while the scan runs.
+  const bool scanner = (int)threadIdx.x < n_scan;
+  const int n_help = (int)blockDim.x - n_scan;
+  const bool piped = n_help > 0;
   const int col = threadIdx.x >> 2, part = threadIdx.x & 3;
   const int hk = h / (a.H / a.G);
   const T* rp = static_cast<const T*>(a.r);
@@ -86,54 +93,55 @@ __global__ void delta_scan_kernel(const DeltaArgs a) {
 #pragma unroll
   for (int e4 = 0; e4 < KPL / 4; ++e4) {
     float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (!fresh && col < Dv) v4 = *reinterpret_cast<const float4*>(my_state + (e4 * 4 + part) * 4);
+    if (scanner && !fresh && col < Dv) v4 = *reinterpret_cast<const float4*>(my_state + (e4 * 4 + part) * 4);
     s[e4 * 4 + 0] = v4.x; s[e4 * 4 + 1] = v4.y; s[e4 * 4 + 2] = v4.z; s[e4 * 4 + 3] = v4.w;
   }
   const float rate = MODE == MODE_GATED ? expf(a.head_rate[h]) : 0.60653065971263342f;   // e^{-1/2}
   const float q_scale = rsqrtf((float)Dk);
 
-  for (int base = t0; base < t1; base += kChunk) {
-    const int n = min(kChunk, t1 - base);
-    // ---- the chunk's vectors, one warp per token
-    for (int c = warp; c < n; c += nwarps) {
+  // ---- a chunk's vectors, one warp per token (warps w0, w0 + nw, ... of the group that prepares)
+  auto prepare = [&](int base, int n, float* buf, int w0, int nw, int th0, int nth) {
+    for (int c = w0; c < n; c += nw) {
       const int t = base + c;
-      float* tok = smem + (size_t)c * tok_floats;
-      float kr_[DKP / 32 > 0 ? DKP / 32 : 1], rr_[DKP / 32 > 0 ? DKP / 32 : 1];
+      float* tok = buf + (size_t)c * tok_floats;
+      constexpr int U = (DKP + 31) / 32;
+      float kr_[U], rr_[U], zd_[U], za_[U];
       float ksum = 0.f, rsum = 0.f;
 #pragma unroll
-      for (int u = 0; u < (DKP + 31) / 32; ++u) {
+      for (int u = 0; u < U; ++u) {                 // every load of the token is under way before the first sum
         const int i = u * 32 + lane;
-        float kv = 0.f, rv = 0.f;
+        float kv = 0.f, rv = 0.f, zd = 0.f, za = 0.f;
         if (i < Dk) {
           kv = to_f32(kp[(size_t)t * a.ld_k + hk * Dk + i]);
           rv = to_f32(rp[(size_t)t * a.ld_r + hk * Dk + i]);
+          zd = to_f32(dp[(size_t)t * a.ld_decay + h * Dk + i]) + a.decay_bias[h * Dk + i];
+          if (MODE == MODE_GENERAL) za = to_f32(xp[(size_t)t * a.ld_aux + h * Dk + i]) + a.aux_bias[h * Dk + i];
         }
-        kr_[u] = kv; rr_[u] = rv;
+        kr_[u] = kv; rr_[u] = rv; zd_[u] = zd; za_[u] = za;
         ksum += kv * kv; rsum += rv * rv;
       }
+      float beta = 1.f;
+      if (MODE == MODE_GATED) beta = sigmoidf_(to_f32(xp[(size_t)t * a.ld_aux + h]));
       ksum = warp_sum(ksum);
       rsum = warp_sum(rsum);
       const float kinv = 1.0f / sqrtf(ksum + 1e-6f);
       const float rinv = MODE == MODE_GATED ? q_scale / sqrtf(rsum + 1e-6f) : 1.0f;
-      float beta = 1.f;
-      if (MODE == MODE_GATED) beta = sigmoidf_(to_f32(xp[(size_t)t * a.ld_aux + h]));
       float pr = 0.f, kr = 0.f;
 #pragma unroll
-      for (int u = 0; u < (DKP + 31) / 32; ++u) {
+      for (int u = 0; u < U; ++u) {
         const int i = u * 32 + lane;
         if (i >= DKP) continue;
         float d = 0.f, p = 0.f, x = 0.f, kk = 0.f, y = 0.f;
         if (i < Dk) {
-          const float zd = to_f32(dp[(size_t)t * a.ld_decay + h * Dk + i]) + a.decay_bias[h * Dk + i];
           if (MODE == MODE_GENERAL) {
             const float unit = kr_[u] * kinv;
-            const float rem = sigmoidf_(to_f32(xp[(size_t)t * a.ld_aux + h * Dk + i]) + a.aux_bias[h * Dk + i]);
-            d = expf(-rate * sigmoidf_(zd));
+            const float rem = sigmoidf_(za_[u]);
+            d = expf(-rate * sigmoidf_(zd_[u]));
             p = rem * unit; x = unit; kk = kr_[u]; y = rr_[u] * d;
             pr += p * rr_[u]; kr += kk * rr_[u];
           } else {
             const float kn = kr_[u] * kinv, qn = rr_[u] * rinv;
-            d = expf(-rate * softplusf_(zd));
+            d = expf(-rate * softplusf_(zd_[u]));
             p = beta * kn; x = kn * d; kk = kn; y = qn * d;
             kr += kn * qn;
           }
@@ -146,7 +154,7 @@ __global__ void delta_scan_kernel(const DeltaArgs a) {
       if (lane == 0) { tok[5 * DKP + 2 * dvp] = pr; tok[5 * DKP + 2 * dvp + 1] = kr; }
     }
     // the chunk's column values c_j
-    for (int idx = threadIdx.x; idx < n * dvp; idx += blockDim.x) {
+    for (int idx = th0; idx < n * dvp; idx += nth) {
       const int c = idx / dvp, j = idx - c * dvp;
       const int t = base + c;
       float cv = 0.f;
@@ -154,48 +162,50 @@ __global__ void delta_scan_kernel(const DeltaArgs a) {
         cv = to_f32(vp[(size_t)t * a.ld_v + h * Dv + j]);
         if (MODE == MODE_GATED) cv *= sigmoidf_(to_f32(xp[(size_t)t * a.ld_aux + h]));
       }
-      smem[(size_t)c * tok_floats + 5 * DKP + j] = cv;
+      buf[(size_t)c * tok_floats + 5 * DKP + j] = cv;
     }
-    __syncthreads();
-    // ---- the scan over the chunk.  Every thread takes part (the shuffles name the whole warp);
-    // threads beyond the last column carry zeros and store nothing.
-    {
-      for (int c = 0; c < n; ++c) {
-        const float* tok = smem + (size_t)c * tok_floats;
-        const float4* D4 = reinterpret_cast<const float4*>(tok);
-        const float4* P4 = reinterpret_cast<const float4*>(tok + DKP);
-        const float4* X4 = reinterpret_cast<const float4*>(tok + 2 * DKP);
-        const float4* K4 = reinterpret_cast<const float4*>(tok + 3 * DKP);
-        const float4* Y4 = reinterpret_cast<const float4*>(tok + 4 * DKP);
-        float dx = 0.f, dy = 0.f;
+  };
+
+  // ---- the scan over a chunk.  Every scanning thread takes part (the shuffles name the whole
+  // warp); threads beyond the last column carry zeros and store nothing.
+  auto scan = [&](int n, float* buf) {
+    for (int c = 0; c < n; ++c) {
+      float* tok = buf + (size_t)c * tok_floats;
+      const float4* D4 = reinterpret_cast<const float4*>(tok);
+      const float4* P4 = reinterpret_cast<const float4*>(tok + DKP);
+      const float4* X4 = reinterpret_cast<const float4*>(tok + 2 * DKP);
+      const float4* K4 = reinterpret_cast<const float4*>(tok + 3 * DKP);
+      const float4* Y4 = reinterpret_cast<const float4*>(tok + 4 * DKP);
+      float dx = 0.f, dy = 0.f;
 #pragma unroll
-        for (int e4 = 0; e4 < KPL / 4; ++e4) {
-          const float4 xv = X4[e4 * 4 + part], yv = Y4[e4 * 4 + part];
-          dx = fmaf(xv.x, s[e4 * 4 + 0], dx); dx = fmaf(xv.y, s[e4 * 4 + 1], dx);
-          dx = fmaf(xv.z, s[e4 * 4 + 2], dx); dx = fmaf(xv.w, s[e4 * 4 + 3], dx);
-          dy = fmaf(yv.x, s[e4 * 4 + 0], dy); dy = fmaf(yv.y, s[e4 * 4 + 1], dy);
-          dy = fmaf(yv.z, s[e4 * 4 + 2], dy); dy = fmaf(yv.w, s[e4 * 4 + 3], dy);
-        }
-        dx += __shfl_xor_sync(0xffffffffu, dx, 1); dy += __shfl_xor_sync(0xffffffffu, dy, 1);
-        dx += __shfl_xor_sync(0xffffffffu, dx, 2); dy += __shfl_xor_sync(0xffffffffu, dy, 2);
-        const float cj = col < dvp ? tok[5 * DKP + col] : 0.f;
-        const float pr = tok[5 * DKP + 2 * dvp], kr = tok[5 * DKP + 2 * dvp + 1];
-        if (part == 0 && col < dvp) smem[(size_t)c * tok_floats + 5 * DKP + dvp + col] = dy - dx * pr + cj * kr;
+      for (int e4 = 0; e4 < KPL / 4; ++e4) {
+        const float4 xv = X4[e4 * 4 + part], yv = Y4[e4 * 4 + part];
+        dx = fmaf(xv.x, s[e4 * 4 + 0], dx); dx = fmaf(xv.y, s[e4 * 4 + 1], dx);
+        dx = fmaf(xv.z, s[e4 * 4 + 2], dx); dx = fmaf(xv.w, s[e4 * 4 + 3], dx);
+        dy = fmaf(yv.x, s[e4 * 4 + 0], dy); dy = fmaf(yv.y, s[e4 * 4 + 1], dy);
+        dy = fmaf(yv.z, s[e4 * 4 + 2], dy); dy = fmaf(yv.w, s[e4 * 4 + 3], dy);
+      }
+      dx += __shfl_xor_sync(0xffffffffu, dx, 1); dy += __shfl_xor_sync(0xffffffffu, dy, 1);
+      dx += __shfl_xor_sync(0xffffffffu, dx, 2); dy += __shfl_xor_sync(0xffffffffu, dy, 2);
+      const float cj = col < dvp ? tok[5 * DKP + col] : 0.f;
+      const float pr = tok[5 * DKP + 2 * dvp], kr = tok[5 * DKP + 2 * dvp + 1];
+      if (part == 0 && col < dvp) tok[5 * DKP + dvp + col] = dy - dx * pr + cj * kr;
 #pragma unroll
-        for (int e4 = 0; e4 < KPL / 4; ++e4) {
-          const float4 dv = D4[e4 * 4 + part], pv = P4[e4 * 4 + part], kv = K4[e4 * 4 + part];
-          s[e4 * 4 + 0] = fmaf(dv.x, s[e4 * 4 + 0], fmaf(kv.x, cj, -pv.x * dx));
-          s[e4 * 4 + 1] = fmaf(dv.y, s[e4 * 4 + 1], fmaf(kv.y, cj, -pv.y * dx));
-          s[e4 * 4 + 2] = fmaf(dv.z, s[e4 * 4 + 2], fmaf(kv.z, cj, -pv.z * dx));
-          s[e4 * 4 + 3] = fmaf(dv.w, s[e4 * 4 + 3], fmaf(kv.w, cj, -pv.w * dx));
-        }
+      for (int e4 = 0; e4 < KPL / 4; ++e4) {
+        const float4 dv = D4[e4 * 4 + part], pv = P4[e4 * 4 + part], kv = K4[e4 * 4 + part];
+        s[e4 * 4 + 0] = fmaf(dv.x, s[e4 * 4 + 0], fmaf(kv.x, cj, -pv.x * dx));
+        s[e4 * 4 + 1] = fmaf(dv.y, s[e4 * 4 + 1], fmaf(kv.y, cj, -pv.y * dx));
+        s[e4 * 4 + 2] = fmaf(dv.z, s[e4 * 4 + 2], fmaf(kv.z, cj, -pv.z * dx));
+        s[e4 * 4 + 3] = fmaf(dv.w, s[e4 * 4 + 3], fmaf(kv.w, cj, -pv.w * dx));
       }
     }
-    __syncthreads();
-    // ---- the chunk's outputs: RMS over the head, weight, sigmoid gate
-    for (int c = warp; c < n; c += nwarps) {
+  };
+
+  // ---- a chunk's outputs: RMS over the head, weight, sigmoid gate; one warp per token
+  auto finish = [&](int base, int n, const float* buf, int w0, int nw) {
+    for (int c = w0; c < n; c += nw) {
       const int t = base + c;
-      const float* o = smem + (size_t)c * tok_floats + 5 * DKP + dvp;
+      const float* o = buf + (size_t)c * tok_floats + 5 * DKP + dvp;
       float ss = 0.f;
       for (int j = lane; j < Dv; j += 32) ss += o[j] * o[j];
       ss = warp_sum(ss);
@@ -206,9 +216,45 @@ __global__ void delta_scan_kernel(const DeltaArgs a) {
         outp[(size_t)t * a.ld_out + h * Dv + j] = from_f32<T>(o[j] * inv * w * g);
       }
     }
+  };
+
+  if (!piped) {
+    // one group of threads does the three phases in turn
+    const int warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int base = t0; base < t1; base += kChunk) {
+      const int n = min(kChunk, t1 - base);
+      prepare(base, n, smem, warp, nwarps, threadIdx.x, blockDim.x);
+      __syncthreads();
+      scan(n, smem);
+      __syncthreads();
+      finish(base, n, smem, warp, nwarps);
+      __syncthreads();
+    }
+  } else {
+    // Two buffers.  In round i the scanning threads walk chunk i while the helpers finish chunk
+    // i - 1 (they read only its outputs, which nobody writes in this round) and prepare chunk
+    // i + 1 in the same buffer (everything but the outputs, which chunk i - 1's scan is done with).
+    const int n_chunks = (t1 - t0 + kChunk - 1) / kChunk;
+    const int hw = ((int)threadIdx.x - n_scan) >> 5, hnw = n_help >> 5, hth = (int)threadIdx.x - n_scan;
+    if (!scanner && n_chunks > 0) prepare(t0, min(kChunk, t1 - t0), smem, hw, hnw, hth, n_help);
     __syncthreads();
+    for (int i = 0; i <= n_chunks; ++i) {
+      if (scanner) {
+        if (i < n_chunks) scan(min(kChunk, t1 - (t0 + i * kChunk)), smem + (size_t)(i & 1) * buf_floats);
+      } else {
+        if (i >= 1) {
+          const int base = t0 + (i - 1) * kChunk;
+          finish(base, min(kChunk, t1 - base), smem + (size_t)((i - 1) & 1) * buf_floats, hw, hnw);
+        }
+        if (i + 1 < n_chunks) {
+          const int base = t0 + (i + 1) * kChunk;
+          prepare(base, min(kChunk, t1 - base), smem + (size_t)((i + 1) & 1) * buf_floats, hw, hnw, hth, n_help);
+        }
+      }
+      __syncthreads();
+    }
   }
-  if (col < Dv) {
+  if (scanner && col < Dv) {
 #pragma unroll
     for (int e4 = 0; e4 < KPL / 4; ++e4)
       *reinterpret_cast<float4*>(my_state + (e4 * 4 + part) * 4) =
@@ -229,14 +275,26 @@ KVB_EXPORT int kvb_delta_key_pad(int Dk) { return Dk >= 1 ? 4 * delta_kpl(Dk) : 
 template <typename T, int KPL, int MODE>
 static int launch_scan(const DeltaArgs& a, int R, cudaStream_t stream) {
   const int dvp = (a.Dv + 3) & ~3;
-  const int threads = ((4 * dvp + 31) / 32) * 32;
-  const size_t smem = (size_t)kChunk * (5 * 4 * KPL + 2 * dvp + 4) * sizeof(float);
+  const int n_scan = ((4 * dvp + 31) / 32) * 32;
+  // up to sixteen warps beside the scanning ones, so that a chunk's sixteen tokens are prepared at once
+  static int max_threads = 0;                 // what the kernel's registers allow in one block
+  if (max_threads == 0) {
+    cudaFuncAttributes attr;
+    cudaError_t e = cudaFuncGetAttributes(&attr, delta_scan_kernel<T, KPL, MODE>);
+    if (e != cudaSuccess) return (int)e;
+    max_threads = attr.maxThreadsPerBlock / 32 * 32;
+  }
+  if (n_scan > max_threads) return KVB_ERR_BAD_SIZE;
+  int n_help = max_threads - n_scan < 512 ? max_threads - n_scan : 512;
+  if (n_help < 128) n_help = 0;               // too few to keep up: the scanning threads do everything in turn
+  const size_t buf = (size_t)kChunk * (5 * 4 * KPL + 2 * dvp + 4) * sizeof(float);
+  const size_t smem = n_help ? 2 * buf : buf;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<T, KPL, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  kvb_launch(delta_scan_kernel<T, KPL, MODE>, dim3(a.H, R), dim3(threads), smem, stream, a);
+  kvb_launch(delta_scan_kernel<T, KPL, MODE>, dim3(a.H, R), dim3(n_scan + n_help), smem, stream, a, n_scan);
   return kvb_launch_result();
 }
 

@@ -329,3 +329,280 @@ KVB_EXPORT int kvb_latent_attention(const void* q_abs, int ld_qa, int hs_qa, con
 #undef KVB_LATENT
   return KVB_ERR_BAD_DTYPE;
 }
+
+// ---------------------------------------------------------------- the same attention on tensor cores (bfloat16)
+// A block takes a tile of up to 64 rows, a row being one (token, head) pair: consecutive tokens
+// of one request, all heads (at most 64 of them; more heads take further blocks along y).  Keys
+// come in chunks of 32 by absolute position.  Per chunk: S = Q K^T by mma.sync m16n8k16 (each of
+// the eight warps 16 rows x 16 keys over all of Dc), the scores go through shared memory to a
+// softmax step of four threads per row (running maximum and sum start at the sink, as above;
+// keys behind a row's own position are masked), the weights come back as bfloat16 and
+// O += P V runs on the same chunk in shared memory, whose first `rank` columns are the values
+// (each warp 16 rows x half of the value columns, accumulators in registers).  A row's result
+// depends on its own query and on the chunks only, not on what else shares its tile.
+constexpr int TC_ROWS = 64, TC_KEYS = 32, TC_THREADS = 256, TC_SPAD = 33, TC_PPAD = 40;
+
+__device__ __forceinline__ void ldsm_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                               unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// NT: tiles of 8 value columns per warp at most (a warp owns half of the value columns): rank <= 16 NT.
+template <int NT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_abs, int ld_qa, int hs_qa,
+                           const __nv_bfloat16* __restrict__ q_raw, int ld_q, int hs_q,
+                           const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_len, int rdims,
+                           const __nv_bfloat16* __restrict__ pages, const int* __restrict__ block_table, int max_pages,
+                           int page_size, int num_pages, const int* __restrict__ positions,
+                           const int* __restrict__ q_start, const int* __restrict__ tiles, int tokens_per_tile,
+                           const float* __restrict__ sink, float scale, __nv_bfloat16* __restrict__ out, int ld_out,
+                           int hs_out, int H, int rank, int rot, int* status) {
+  extern __shared__ uint4 tc_smem4[];
+  const int Dc = rank + rot, DcP = Dc + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(tc_smem4);              // [64][DcP]
+  __nv_bfloat16* Ks = Qs + TC_ROWS * DcP;                                       // [32][DcP]
+  __nv_bfloat16* Ps = Ks + TC_KEYS * DcP;                                       // [64][TC_PPAD]
+  float* Ss = reinterpret_cast<float*>(Ps + TC_ROWS * TC_PPAD);                 // [64][TC_SPAD]
+  float* m_s = Ss + TC_ROWS * TC_SPAD;
+  float* l_s = m_s + TC_ROWS;
+  float* corr_s = l_s + TC_ROWS;
+  int* pos_s = reinterpret_cast<int*>(corr_s + TC_ROWS);
+  __shared__ long long row_of[TC_KEYS];
+
+  pdl_trigger();
+  pdl_wait();
+  int req, first, ntok;
+  if (tiles != nullptr) {
+    req = tiles[4 * blockIdx.x]; first = tiles[4 * blockIdx.x + 1]; ntok = tiles[4 * blockIdx.x + 2];
+  } else {
+    req = blockIdx.x; first = q_start[req]; ntok = q_start[req + 1] - first;
+  }
+  ntok = min(ntok, tokens_per_tile);
+  const int h0 = blockIdx.y * TC_ROWS;
+  const int HB = min(TC_ROWS, H - h0);
+  const int rows_used = ntok * HB;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int* table = block_table + (size_t)req * max_pages;
+  const int half = rdims >> 1;
+
+  // the tile's queries: absorbed plain part as it is, the rotated part turned here
+  for (int r = warp; r < TC_ROWS; r += TC_THREADS / 32) {
+    __nv_bfloat16* q = Qs + (size_t)r * DcP;
+    if (r >= rows_used) {
+      for (int i = lane; i < DcP; i += 32) q[i] = __float2bfloat16_rn(0.f);
+      if (lane == 0) { pos_s[r] = -1; m_s[r] = 0.f; l_s[r] = 1.f; }
+      continue;
+    }
+    const int tl = r / HB, hh = h0 + r - tl * HB;
+    const int tr = first + tl;
+    const int pos = positions[tr];
+    const bool bad_pos = rdims > 0 && (pos < 0 || pos >= table_len);
+    if (bad_pos && lane == 0) atomicCAS(status, 0, KVB_STATUS_BAD_POSITION);
+    const __nv_bfloat16* qa = q_abs + (size_t)tr * ld_qa + (size_t)hh * hs_qa;
+    for (int i = lane; i < rank; i += 32) q[i] = qa[i];
+    const __nv_bfloat16* qr = q_raw + (size_t)tr * ld_q + (size_t)hh * hs_q;
+    for (int i = lane; i < half; i += 32) {
+      float c = 1.f, sn = 0.f;
+      if (!bad_pos) { c = cos_t[(size_t)pos * half + i]; sn = sin_t[(size_t)pos * half + i]; }
+      const float u = __bfloat162float(qr[2 * i]), v = __bfloat162float(qr[2 * i + 1]);
+      q[rank + 2 * i] = __float2bfloat16_rn(u * c - v * sn);
+      q[rank + 2 * i + 1] = __float2bfloat16_rn(v * c + u * sn);
+    }
+    for (int i = rdims + lane; i < rot; i += 32) q[rank + i] = qr[i];
+    for (int i = Dc + lane; i < DcP; i += 32) q[i] = __float2bfloat16_rn(0.f);
+    if (lane == 0) { pos_s[r] = pos; m_s[r] = sink[hh]; l_s[r] = 1.f; }
+  }
+  const int max_pos = ntok > 0 ? positions[first + ntok - 1] : -1;
+
+  const int g = lane >> 2, t4 = lane & 3;
+  const int mrow = (warp & 3) * 16;
+  const int nt_used = rank / 16;                 // tiles of 8 columns in this warp's half of the values
+  const int ncol0 = (warp >> 2) * (rank / 2);
+  float acc[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+
+  for (int c0 = 0; c0 <= max_pos; c0 += TC_KEYS) {
+    const int n_keys = min(TC_KEYS, max_pos - c0 + 1);
+    __syncthreads();                               // the chunk before is used up (first round: Qs and the row state are written)
+    if (tid < TC_KEYS) {
+      long long off = -1;
+      if (tid < n_keys) {
+        const int j = c0 + tid;
+        const int lp = j / page_size;
+        const int page = lp < max_pages ? table[lp] : -1;
+        if (page < 0 || page >= num_pages) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+        else off = ((long long)page * page_size + (j % page_size)) * Dc;
+      }
+      row_of[tid] = off;
+    }
+    __syncthreads();
+    const int vecs = Dc >> 3;                      // 16-byte pieces per row
+    for (int j = warp; j < TC_KEYS; j += TC_THREADS / 32) {
+      const long long off = row_of[j];
+      uint4* dst = reinterpret_cast<uint4*>(Ks + (size_t)j * DcP);
+      const uint4* src = reinterpret_cast<const uint4*>(pages + (off >= 0 ? off : 0));
+      for (int v = lane; v < vecs; v += 32) dst[v] = off >= 0 ? src[v] : make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
+    // ---- scores: this warp's 16 rows against 16 of the chunk's keys
+    {
+      const int kcol = (warp >> 2) * 16;
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+      const __nv_bfloat16* a_ptr = Qs + (size_t)(mrow + (lane & 15)) * DcP + (lane >> 4) * 8;
+      const __nv_bfloat16* b_ptr = Ks + (size_t)(kcol + ((lane >> 4) << 3) + (lane & 7)) * DcP + ((lane >> 3) & 1) * 8;
+      for (int ks = 0; ks < Dc; ks += 16) {
+        unsigned a0, a1, a2, a3, b0, b1, b2, b3;
+        ldsm_x4(a0, a1, a2, a3, a_ptr + ks);
+        ldsm_x4(b0, b1, b2, b3, b_ptr + ks);
+        mma_bf16_16816(s0, a0, a1, a2, a3, b0, b1);
+        mma_bf16_16816(s1, a0, a1, a2, a3, b2, b3);
+      }
+      float* srow = Ss + (size_t)(mrow + g) * TC_SPAD + kcol + 2 * t4;
+      srow[0] = s0[0] * scale; srow[1] = s0[1] * scale; srow[8] = s1[0] * scale; srow[9] = s1[1] * scale;
+      srow += 8 * TC_SPAD;
+      srow[0] = s0[2] * scale; srow[1] = s0[3] * scale; srow[8] = s1[2] * scale; srow[9] = s1[3] * scale;
+    }
+    __syncthreads();
+    // ---- softmax step: four threads per row, eight keys each
+    {
+      const int row = tid >> 2, k0 = (tid & 3) * 8;
+      const int pos_r = pos_s[row];
+      float sv[8], mx = -CUDART_INF_F;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int kk = k0 + e;
+        const bool valid = kk < n_keys && c0 + kk <= pos_r && row_of[kk] >= 0;
+        sv[e] = valid ? Ss[(size_t)row * TC_SPAD + kk] : -CUDART_INF_F;
+        mx = fmaxf(mx, sv[e]);
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_old = m_s[row];
+      const float m_new = fmaxf(m_old, mx);
+      float psum = 0.f;
+      __nv_bfloat16* prow = Ps + (size_t)row * TC_PPAD + k0;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float p = sv[e] == -CUDART_INF_F ? 0.f : expf(sv[e] - m_new);
+        psum += p;
+        prow[e] = __float2bfloat16_rn(p);
+      }
+      psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+      psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+      if ((tid & 3) == 0) {
+        const float corr = expf(m_old - m_new);
+        m_s[row] = m_new;
+        l_s[row] = l_s[row] * corr + psum;
+        corr_s[row] = corr;
+      }
+    }
+    __syncthreads();
+    // ---- O = O * corr + P V for this warp's 16 rows and its half of the value columns
+    {
+      const float c_lo = corr_s[mrow + g], c_hi = corr_s[mrow + g + 8];
+#pragma unroll
+      for (int n = 0; n < NT; ++n) { acc[n][0] *= c_lo; acc[n][1] *= c_lo; acc[n][2] *= c_hi; acc[n][3] *= c_hi; }
+      const __nv_bfloat16* a_ptr = Ps + (size_t)(mrow + (lane & 15)) * TC_PPAD + (lane >> 4) * 8;
+      const __nv_bfloat16* b_ptr = Ks + (size_t)(((lane >> 3) & 1) * 8 + (lane & 7)) * DcP + ncol0 + (lane >> 4) * 8;
+#pragma unroll
+      for (int ks = 0; ks < TC_KEYS; ks += 16) {
+        unsigned a0, a1, a2, a3;
+        ldsm_x4(a0, a1, a2, a3, a_ptr + ks);
+#pragma unroll
+        for (int np = 0; np < NT / 2; ++np) {
+          if (2 * np < nt_used) {
+            unsigned b0, b1, b2, b3;
+            ldsm_x4_trans(b0, b1, b2, b3, b_ptr + (size_t)ks * DcP + np * 16);
+            mma_bf16_16816(acc[2 * np], a0, a1, a2, a3, b0, b1);
+            mma_bf16_16816(acc[2 * np + 1], a0, a1, a2, a3, b2, b3);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int hrow = 0; hrow < 2; ++hrow) {
+    const int r = mrow + g + 8 * hrow;
+    if (r >= rows_used) continue;
+    const int tl = r / HB, hh = h0 + r - tl * HB;
+    const float inv = 1.0f / l_s[r];
+    __nv_bfloat16* o = out + (size_t)(first + tl) * ld_out + (size_t)hh * hs_out + ncol0 + 2 * t4;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      if (n < nt_used) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(acc[n][2 * hrow] * inv, acc[n][2 * hrow + 1] * inv);
+        *reinterpret_cast<__nv_bfloat162*>(o + n * 8) = v;
+      }
+    }
+  }
+}
+
+// Rows of (token, head) pairs per tile: tokens per tile for a number of heads.
+KVB_EXPORT int kvb_latent_attention_tc_tokens_per_tile(int H) { return H >= TC_ROWS ? 1 : TC_ROWS / H; }
+
+// Whether the tensor-core form takes these sizes: rank a multiple of 32 up to 512, rank + rot a multiple of 16.
+KVB_EXPORT int kvb_latent_attention_tc_supported(int rank, int rot) {
+  return rank >= 32 && rank <= 512 && rank % 32 == 0 && (rank + rot) % 16 == 0 ? 1 : 0;
+}
+
+template <int NT>
+static int launch_latent_tc(const void* q_abs, int ld_qa, int hs_qa, const void* q_raw, int ld_q, int hs_q,
+                            const float* cos_t, const float* sin_t, int table_len, int rdims, const void* pages,
+                            const int* block_table, int max_pages, int page_size, int num_pages, const int* positions,
+                            const int* q_start, const int* tiles, int n_tiles, const float* sink, float scale, void* out,
+                            int ld_out, int hs_out, int H, int rank, int rot, int* status, cudaStream_t stream) {
+  const int DcP = rank + rot + 8;
+  const size_t smem = (size_t)(TC_ROWS + TC_KEYS) * DcP * 2 + (size_t)TC_ROWS * TC_PPAD * 2 +
+                      (size_t)TC_ROWS * TC_SPAD * 4 + 4 * TC_ROWS * 4;
+  if (smem > 220 * 1024) return KVB_ERR_BAD_SIZE;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_tc_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  using B = __nv_bfloat16;
+  kvb_launch(latent_attention_tc_kernel<NT>, dim3(n_tiles, (H + TC_ROWS - 1) / TC_ROWS), dim3(TC_THREADS), smem, stream,
+             (const B*)q_abs, ld_qa, hs_qa, (const B*)q_raw, ld_q, hs_q, cos_t, sin_t, table_len, rdims, (const B*)pages,
+             block_table, max_pages, page_size, num_pages, positions, q_start, tiles,
+             kvb_latent_attention_tc_tokens_per_tile(H), sink, scale, (B*)out, ld_out, hs_out, H, rank, rot, status);
+  return kvb_launch_result();
+}
+
+// tiles: [n_tiles, 4] int32 rows (request row, first token row, tokens, 0) of at most
+// kvb_latent_attention_tc_tokens_per_tile(H) tokens each, or null: one tile per request (n_tiles requests, each
+// bringing at most that many tokens).  Everything 16-byte aligned: the cache, and rows of rank + rot elements.
+KVB_EXPORT int kvb_latent_attention_tc(const void* q_abs, int ld_qa, int hs_qa, const void* q_raw, int ld_q, int hs_q,
+                                       const float* cos_t, const float* sin_t, int table_len, int rdims,
+                                       const void* pages, const int* block_table, int max_pages, int page_size,
+                                       int num_pages, const int* positions, const int* q_start, const int* tiles,
+                                       int n_tiles, const float* sink, float scale, void* out, int ld_out, int hs_out,
+                                       int H, int rank, int rot, int* status, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (!kvb_latent_attention_tc_supported(rank, rot) || H < 1 || (rdims & 1) || rdims > rot) return KVB_ERR_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(pages) & 15) || (reinterpret_cast<uintptr_t>(out) & 3) || (ld_out & 1) || (hs_out & 1))
+    return KVB_ERR_ALIGN;
+#define KVB_LATENT_TC(NT)                                                                                            \
+  return launch_latent_tc<NT>(q_abs, ld_qa, hs_qa, q_raw, ld_q, hs_q, cos_t, sin_t, table_len, rdims, pages,        \
+                              block_table, max_pages, page_size, num_pages, positions, q_start, tiles, n_tiles, sink, \
+                              scale, out, ld_out, hs_out, H, rank, rot, status, stream)
+  if (rank <= 64) { KVB_LATENT_TC(4); }
+  if (rank <= 128) { KVB_LATENT_TC(8); }
+  if (rank <= 256) { KVB_LATENT_TC(16); }
+  KVB_LATENT_TC(32);
+#undef KVB_LATENT_TC
+}

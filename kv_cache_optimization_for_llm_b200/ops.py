@@ -73,6 +73,40 @@ def _check(rc: int, what: str) -> None:
             raise KernelError(f"{what}: {_ERR.get(rc, rc)}")
         raise KernelError(f"{what}: CUDA error {rc} ({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
     launch_count += 1
+    if _marks is not None:
+        _mark(what)
+
+
+_marks = None      # while a step is being timed operator by operator: [(name, event after its launch)]
+
+
+def _mark(name: str) -> None:
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record()
+    _marks.append((name, ev))
+
+
+class timed_operators:
+    """While active, an event is recorded behind every launch of this package and behind every
+    library product; ``times`` afterwards maps operator name -> (launches, milliseconds), each
+    interval running from the event before to the operator's own.  For steps whose kernels are
+    long enough that the host is not the bound (prompt portions); not inside a graph capture."""
+
+    def __enter__(self):
+        global _marks
+        _marks = []
+        _mark("start")
+        return self
+
+    def __exit__(self, *exc):
+        global _marks
+        marks, _marks = _marks, None
+        torch.cuda.synchronize()
+        self.times = {}
+        for (_, before), (name, ev) in zip(marks, marks[1:]):
+            n, ms = self.times.get(name, (0, 0.0))
+            self.times[name] = (n + 1, ms + before.elapsed_time(ev))
+        return False
 
 
 _step_stream: Optional[c_void_p] = None     # the stream of the running forward pass, looked up once
@@ -578,7 +612,10 @@ def _library_product(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -
     global _mm_takes_out_with_dtype
     out = new((x.shape[0], w.shape[0]), out_dtype, x.device)
     if out_dtype == x.dtype:
-        return torch.matmul(x, w.t(), out=out)
+        torch.matmul(x, w.t(), out=out)
+        if _marks is not None:
+            _mark("library_product")
+        return out
     if _mm_takes_out_with_dtype:
         try:
             return torch.mm(x, w.t(), out_dtype=out_dtype, out=out)
