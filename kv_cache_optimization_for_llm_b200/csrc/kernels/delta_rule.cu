@@ -176,15 +176,17 @@ __global__ void delta_scan_kernel(const DeltaArgs a, int n_scan) {
       const float4* X4 = reinterpret_cast<const float4*>(tok + 2 * DKP);
       const float4* K4 = reinterpret_cast<const float4*>(tok + 3 * DKP);
       const float4* Y4 = reinterpret_cast<const float4*>(tok + 4 * DKP);
-      float dx = 0.f, dy = 0.f;
+      // four partial sums per dot product: the chain of dependent additions is KPL / 4 long, not KPL
+      float dx0 = 0.f, dx1 = 0.f, dx2 = 0.f, dx3 = 0.f, dy0 = 0.f, dy1 = 0.f, dy2 = 0.f, dy3 = 0.f;
 #pragma unroll
       for (int e4 = 0; e4 < KPL / 4; ++e4) {
         const float4 xv = X4[e4 * 4 + part], yv = Y4[e4 * 4 + part];
-        dx = fmaf(xv.x, s[e4 * 4 + 0], dx); dx = fmaf(xv.y, s[e4 * 4 + 1], dx);
-        dx = fmaf(xv.z, s[e4 * 4 + 2], dx); dx = fmaf(xv.w, s[e4 * 4 + 3], dx);
-        dy = fmaf(yv.x, s[e4 * 4 + 0], dy); dy = fmaf(yv.y, s[e4 * 4 + 1], dy);
-        dy = fmaf(yv.z, s[e4 * 4 + 2], dy); dy = fmaf(yv.w, s[e4 * 4 + 3], dy);
+        dx0 = fmaf(xv.x, s[e4 * 4 + 0], dx0); dx1 = fmaf(xv.y, s[e4 * 4 + 1], dx1);
+        dx2 = fmaf(xv.z, s[e4 * 4 + 2], dx2); dx3 = fmaf(xv.w, s[e4 * 4 + 3], dx3);
+        dy0 = fmaf(yv.x, s[e4 * 4 + 0], dy0); dy1 = fmaf(yv.y, s[e4 * 4 + 1], dy1);
+        dy2 = fmaf(yv.z, s[e4 * 4 + 2], dy2); dy3 = fmaf(yv.w, s[e4 * 4 + 3], dy3);
       }
+      float dx = (dx0 + dx1) + (dx2 + dx3), dy = (dy0 + dy1) + (dy2 + dy3);
       dx += __shfl_xor_sync(0xffffffffu, dx, 1); dy += __shfl_xor_sync(0xffffffffu, dy, 1);
       dx += __shfl_xor_sync(0xffffffffu, dx, 2); dy += __shfl_xor_sync(0xffffffffu, dy, 2);
       const float cj = col < dvp ? tok[5 * DKP + col] : 0.f;
@@ -273,7 +275,7 @@ static int delta_kpl(int Dk) {
 KVB_EXPORT int kvb_delta_key_pad(int Dk) { return Dk >= 1 ? 4 * delta_kpl(Dk) : 0; }
 
 template <typename T, int KPL, int MODE>
-static int launch_scan(const DeltaArgs& a, int R, cudaStream_t stream) {
+static int launch_scan(const DeltaArgs& a, int R, int max_run, cudaStream_t stream) {
   const int dvp = (a.Dv + 3) & ~3;
   const int n_scan = ((4 * dvp + 31) / 32) * 32;
   // up to sixteen warps beside the scanning ones, so that a chunk's sixteen tokens are prepared at once
@@ -287,6 +289,7 @@ static int launch_scan(const DeltaArgs& a, int R, cudaStream_t stream) {
   if (n_scan > max_threads) return KVB_ERR_BAD_SIZE;
   int n_help = max_threads - n_scan < 512 ? max_threads - n_scan : 512;
   if (n_help < 128) n_help = 0;               // too few to keep up: the scanning threads do everything in turn
+  if (max_run > 0 && max_run <= kChunk) n_help = 0;   // a single chunk per request (decode steps): nothing to overlap
   const size_t buf = (size_t)kChunk * (5 * 4 * KPL + 2 * dvp + 4) * sizeof(float);
   const size_t smem = n_help ? 2 * buf : buf;
   if (smem > 48 * 1024) {
@@ -299,28 +302,29 @@ static int launch_scan(const DeltaArgs& a, int R, cudaStream_t stream) {
 }
 
 template <typename T, int MODE>
-static int launch_scan_kpl(const DeltaArgs& a, int R, cudaStream_t stream) {
+static int launch_scan_kpl(const DeltaArgs& a, int R, int max_run, cudaStream_t stream) {
   switch (delta_kpl(a.Dk)) {
-    case 4: return launch_scan<T, 4, MODE>(a, R, stream);
-    case 8: return launch_scan<T, 8, MODE>(a, R, stream);
-    case 16: return launch_scan<T, 16, MODE>(a, R, stream);
-    case 32: return launch_scan<T, 32, MODE>(a, R, stream);
+    case 4: return launch_scan<T, 4, MODE>(a, R, max_run, stream);
+    case 8: return launch_scan<T, 8, MODE>(a, R, max_run, stream);
+    case 16: return launch_scan<T, 16, MODE>(a, R, max_run, stream);
+    case 32: return launch_scan<T, 32, MODE>(a, R, max_run, stream);
   }
   return KVB_ERR_BAD_SIZE;
 }
 
-// Refuses: Dk > 128, Dv > 256, Dv > 128 together with Dk > 64 (a thread's quarter column would
-// not stay in registers), heads that do not group evenly.
-KVB_EXPORT int kvb_delta_scan(const DeltaArgs* args, int mode, int R, int dtype, cudaStream_t stream) {
+// max_run: the longest run of tokens among the requests if the host knows it (0: unknown); the
+// results do not depend on it.  Refuses: Dk > 128, Dv > 256, Dv > 128 together with Dk > 64 (a
+// thread's quarter column would not stay in registers), heads that do not group evenly.
+KVB_EXPORT int kvb_delta_scan(const DeltaArgs* args, int mode, int R, int max_run, int dtype, cudaStream_t stream) {
   const DeltaArgs& a = *args;
   if (R <= 0) return 0;
   if (a.Dk < 1 || a.Dk > 128 || a.Dv < 1 || a.Dv > 256 || (a.Dk > 64 && a.Dv > 128)) return KVB_ERR_BAD_SIZE;
   if (a.G < 1 || a.H % a.G || R > 65535) return KVB_ERR_BAD_SIZE;
   if (mode != MODE_GENERAL && mode != MODE_GATED) return KVB_ERR_BAD_SIZE;
   if (mode == MODE_GENERAL) {
-    KVB_DISPATCH_DTYPE(dtype, T, return (launch_scan_kpl<T, MODE_GENERAL>(a, R, stream)));
+    KVB_DISPATCH_DTYPE(dtype, T, return (launch_scan_kpl<T, MODE_GENERAL>(a, R, max_run, stream)));
   } else {
-    KVB_DISPATCH_DTYPE(dtype, T, return (launch_scan_kpl<T, MODE_GATED>(a, R, stream)));
+    KVB_DISPATCH_DTYPE(dtype, T, return (launch_scan_kpl<T, MODE_GATED>(a, R, max_run, stream)));
   }
   return KVB_ERR_BAD_DTYPE;
 }

@@ -400,7 +400,8 @@ def delta_scan(mode: str, batch, state: torch.Tensor, r, k, v, gate, decay, aux,
     a.q_start, a.req_start, a.slots = batch.q_start.data_ptr(), batch.req_start.data_ptr(), batch.slots.data_ptr()
     a.H, a.G, a.Dk, a.Dv, a.eps = heads, key_heads, dk, dv, eps
     rc = lib("delta_rule").kvb_delta_scan(ctypes.byref(a), c_int({"general": 0, "gated": 1}[mode]),
-                                          c_int(batch.num_reqs), c_int(dtype_code(x0.dtype)), _stream())
+                                          c_int(batch.num_reqs), c_int(int(getattr(batch, "max_q_len", 0) or 0)),
+                                          c_int(dtype_code(x0.dtype)), _stream())
     _check(rc, "delta_scan")
     choices["delta_scan_" + mode] += 1
     return out
@@ -462,6 +463,50 @@ def head_gemm(x: torch.Tensor, first: int, head_stride: int, w: torch.Tensor) ->
     return out
 
 
+LATENT_TC = os.environ.get('KVB200_LATENT_TC', '1') != '0'
+_latent_tc_ok: Dict[tuple, bool] = {}
+_latent_tpt: Dict[int, int] = {}
+
+
+def latent_attention_tc_supported(rank: int, rot: int) -> bool:
+    """Whether the tensor-core form of the latent attention takes these sizes (bfloat16 only)."""
+    key = (int(rank), int(rot))
+    if key not in _latent_tc_ok:
+        _latent_tc_ok[key] = bool(lib("latent_attention").kvb_latent_attention_tc_supported(c_int(key[0]), c_int(key[1])))
+    return _latent_tc_ok[key]
+
+
+def latent_tokens_per_tile(heads: int) -> int:
+    """Tokens in one tile of the tensor-core latent attention (a tile holds up to 64 (token, head) rows)."""
+    if heads not in _latent_tpt:
+        _latent_tpt[heads] = int(lib("latent_attention").kvb_latent_attention_tc_tokens_per_tile(c_int(int(heads))))
+    return _latent_tpt[heads]
+
+
+def _query_tiles(batch, nt: int) -> torch.Tensor:
+    """[n, 4] int32 tiles (request row, first token row, tokens, 0) of at most ``nt`` consecutive tokens of one
+    request: the ones the batch was laid out with, or built here for a batch that was made without them."""
+    ready = (getattr(batch, "tiles", None) or {}).get(nt)
+    if ready is not None:
+        return ready
+    cache = batch.host.setdefault("query_tiles", {})
+    got = cache.get(nt)
+    if got is None:
+        import numpy as np
+        qs = batch.host["q_start"]
+        rows = []
+        for r in range(batch.num_reqs):
+            a, b = int(qs[r]), int(qs[r + 1])
+            starts = np.arange(a, b, nt, dtype=np.int32)
+            tile = np.zeros((len(starts), 4), dtype=np.int32)
+            tile[:, 0], tile[:, 1], tile[:, 2] = r, starts, np.minimum(nt, b - starts)
+            rows.append(tile)
+        host = torch.from_numpy(np.concatenate(rows)).pin_memory()
+        got = host.to(batch.token_ids.device, non_blocking=True)
+        cache[nt], cache[("host", nt)] = got, host      # the pinned source lives until the step is over
+    return got
+
+
 def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, rot_first: int, q_head_stride: int, cos, sin, rdims: int,
                      pages: torch.Tensor, block_table, batch, sink: torch.Tensor, scale: float, heads: int,
                      rank: int, rot: int) -> torch.Tensor:
@@ -473,6 +518,22 @@ def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, rot_first: int, q_hea
     assert q_abs.is_contiguous() and q.stride(1) == 1 and pages.is_contiguous() and sink.dtype == torch.float32
     T = q_abs.shape[0]
     out = new((T, heads * rank), q_abs.dtype, q_abs.device)
+    if q_abs.dtype == torch.bfloat16 and LATENT_TC and latent_attention_tc_supported(rank, rot):
+        nt = latent_tokens_per_tile(heads)
+        if batch.decode_only:
+            tiles, n_tiles = None, batch.num_reqs           # one tile per request, found in the kernel
+        else:
+            tiles = _query_tiles(batch, nt)
+            n_tiles = tiles.shape[0]
+        rc = lib("latent_attention").kvb_latent_attention_tc(
+            _p(q_abs), c_int(q_abs.stride(0)), c_int(rank), c_void_p(_at(q, rot_first)), c_int(q.stride(0)),
+            c_int(q_head_stride), _p(cos), _p(sin), c_int(0 if cos is None else cos.shape[0]), c_int(rdims), _p(pages),
+            _p(block_table), c_int(block_table.shape[1]), c_int(pages.shape[2]), c_int(pages.shape[0]),
+            _p(batch.positions), _p(batch.q_start), _p(tiles), c_int(n_tiles), _p(sink), c_float(scale), _p(out),
+            c_int(out.stride(0)), c_int(rank), c_int(heads), c_int(rank), c_int(rot), _p(batch.status), _stream())
+        _check(rc, "latent_attention_tc")
+        choices["latent_attention_tc"] += 1
+        return out
     rc = lib("latent_attention").kvb_latent_attention(
         _p(q_abs), c_int(q_abs.stride(0)), c_int(rank), c_void_p(_at(q, rot_first)), c_int(q.stride(0)),
         c_int(q_head_stride), _p(cos), _p(sin), c_int(0 if cos is None else cos.shape[0]), c_int(rdims), _p(pages),

@@ -72,6 +72,13 @@ class LatentAttention(Part):
         return [self.w_in.shape[0], self.q_rank, H * (self.dim + self.rot), 2 * H * self.rank, H * self.vdim,
                 self.o.shape[0]]
 
+    def query_tile_heights(self):
+        """Tokens per tile of the tensor-core attention (bfloat16, sizes it takes): the step's batch
+        lays the tiles out for it."""
+        if self.ctx.dtype != torch.bfloat16 or not ops.LATENT_TC or not ops.latent_attention_tc_supported(self.rank, self.rot):
+            return []
+        return [ops.latent_tokens_per_tile(self.heads)]
+
     def forward(self, x, batch, cache):
         d = ops.linear(x, self.w_in)
         cos, sin = self.position.tables() if self.position is not None else (None, None)

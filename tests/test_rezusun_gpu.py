@@ -271,7 +271,13 @@ def _latent_mixer(mx, wt, ctx, H):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("shape", [dict(), dict(heads=9, dim=8, rot_dim=4, vdim=8, q_rank=12, kv_rank=10),
                                    dict(heads=2, dim=32, rot_dim=16, vdim=16, q_rank=24, kv_rank=72, rot_dims=8),
-                                   dict(heads=1, dim=16, rot_dim=64, vdim=8, q_rank=8, kv_rank=200, base=77.0)])
+                                   dict(heads=1, dim=16, rot_dim=64, vdim=8, q_rank=8, kv_rank=200, base=77.0),
+                                   # sizes that the tensor-core form takes in bfloat16: three tokens of 20 heads to a
+                                   # tile, more heads than one tile has rows, a latent between two of its sizes
+                                   dict(heads=3, dim=16, rot_dim=16, vdim=8, q_rank=16, kv_rank=32),
+                                   dict(heads=20, dim=8, rot_dim=32, vdim=8, q_rank=8, kv_rank=96, rot_dims=12),
+                                   dict(heads=70, dim=8, rot_dim=16, vdim=4, q_rank=8, kv_rank=64),
+                                   dict(heads=4, dim=8, rot_dim=16, vdim=8, q_rank=8, kv_rank=160)])
 def test_latent_attention_alone_in_portions_and_beside_another_request(dtype, shape):
     """Several shapes (more heads than a block takes, a rotary part of which only some dimensions
     turn, latents wider than one pass over the lanes), 70 and 33 tokens on pages of 8 that lie
@@ -286,9 +292,13 @@ def test_latent_attention_alone_in_portions_and_beside_another_request(dtype, sh
     for r, T in enumerate((70, 33)):
         x, x64 = _w(rng, (T, H), 1.0)
         xs[r], refs[r] = x.to(DT[dtype]).cuda(), R.latent_attention(x64, w64, "", mx, 1e-5)
+    from kv_cache_optimization_for_llm_b200 import ops
+    before = ops.choices["latent_attention_tc"]
     whole = _run_in_steps(mixer, ctx, xs, [[(0, 70)], [(1, 33)]])
     cut = _run_in_steps(mixer, ctx, xs, [[(0, 8), (1, 1)], [(0, 9), (1, 1)], [(0, 2), (1, 30)], [(0, 1), (1, 1)],
                                          [(0, 44)], [(0, 1)], [(0, 1)], [(0, 4)]])
+    on_tensor_cores = dtype == "bfloat16" and mx["kv_rank"] % 32 == 0 and (mx["kv_rank"] + mx["rot_dim"]) % 16 == 0
+    assert (ops.choices["latent_attention_tc"] > before) == on_tensor_cores
     for r in xs:
         assert _rel(whole[r], refs[r]) < TOL[dtype]
         assert _rel(cut[r], refs[r]) < TOL[dtype]
@@ -296,7 +306,8 @@ def test_latent_attention_alone_in_portions_and_beside_another_request(dtype, sh
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_latent_attention_finds_one_far_key_and_counts_the_sink_once(dtype):
+@pytest.mark.parametrize("kv_rank", [16, 32])
+def test_latent_attention_finds_one_far_key_and_counts_the_sink_once(dtype, kv_rank):
     """300 tokens; the shared key part of token 5 is blown up so that, for late queries, its score
     stands out among hundreds (random keys would hide a lost page or a wrong block table).  The
     plain result changes by a large factor when that key is taken away, and when the sink is;
@@ -304,7 +315,8 @@ def test_latent_attention_finds_one_far_key_and_counts_the_sink_once(dtype):
     rng = np.random.default_rng(11)
     ctx = _ctx(dtype)
     H, T = 40, 300
-    mx = tiny.latent(heads=2, dim=8, rot_dim=8, vdim=8, q_rank=12, kv_rank=16, base=1e6)["mixer"]
+    # a latent of 32 with a rotated part of 16 runs on tensor cores in bfloat16, a latent of 16 does not
+    mx = tiny.latent(heads=2, dim=8, rot_dim=8 if kv_rank == 16 else 16, vdim=8, q_rank=12, kv_rank=kv_rank, base=1e6)["mixer"]
     wt, w64 = _latent_weights(rng, H, mx)
     wt["sink"], w64["sink"] = _w(rng, (2,), 0.1, 4.0)
     x, x64 = _w(rng, (T, H), 1.0)

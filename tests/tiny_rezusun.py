@@ -31,9 +31,10 @@ def config(layers, width=48, vocab=101, loop=None, eps=1e-5):
             "loop": loop}
 
 
-# mixes every kind, a repeated run of two layers, a feed-forward on a delta layer, a layer with one tap
+# mixes every kind, a repeated run of two layers, a feed-forward on a delta layer, a layer with one tap; the
+# first attention layer's sizes keep it on the plain kernel in bfloat16, the last one's put it on tensor cores
 MIXED = config([general(), channel(ff=40), latent(ff=56), channel(heads=2, kv_heads=2, dim=8, vdim=8, conv=1),
-                general(heads=3, dim=20, rank=9), latent(heads=2, dim=8, rot_dim=4, vdim=8, q_rank=12, kv_rank=10)],
+                general(heads=3, dim=20, rank=9), latent(heads=2, dim=8, rot_dim=16, vdim=8, q_rank=12, kv_rank=32)],
                loop={"start": 1, "stop": 3, "times": 2})
 
 
