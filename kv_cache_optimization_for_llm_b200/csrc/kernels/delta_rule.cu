@@ -16,11 +16,14 @@
 // y = r * d the read-out is  o_j = y.s_j - (x.s_j)(p.r) + c_j (k.r)  over the state before the
 // token, so one round of shuffles per token serves both the update and the read-out.
 //
-// A block owns one (head, request): it walks the request's tokens of this step in chunks of
-// 16.  A chunk is prepared (its projections become the float32 vectors above, one warp per
-// token), scanned (the threads that own the columns step through it) and finished (RMS over
-// the head, weight, sigmoid gate); up to sixteen more warps prepare chunk i + 1 and finish
-// chunk i - 1 while the scan walks chunk i, in two buffers, one block barrier per chunk.  The state is read from the request's
+// A block owns the columns (or, when the grid would leave SMs idle, a share of the columns) of
+// one (head, request): it walks the request's tokens of this step in chunks of 16.  A chunk is
+// prepared (its projections become the float32 vectors above, one warp per token) and scanned
+// (the threads that own the columns step through it and leave the read-outs in a float32
+// scratch); up to sixteen more warps prepare chunk i + 1 while the scan walks chunk i, in two
+// buffers, one block barrier per chunk.  A second small kernel norms each head's read-out (RMS,
+// weight, sigmoid gate).  The scan is bound by shared memory: every column re-reads the token's
+// five vectors, which is why a head's columns are spread over several SMs when there is room.  The state is read from the request's
 // slot at the start (zero when the request starts at position 0) and written back at the end.
 // Everything but the projections is float32.  A token's result does not depend on how the
 // request was cut into steps: each token is prepared alone and the scan is sequential.
@@ -53,13 +56,14 @@ struct DeltaArgs {
   const int* slots;                 // [R]
   int H, G, Dk, Dv;
   float eps;
+  float* o_raw;                     // [T, H * Dv] float32 scratch: the read-outs before their norm
 };
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 template <typename T, int KPL, int MODE>
-__global__ void delta_scan_kernel(const DeltaArgs a, int n_scan) {
+__global__ void delta_scan_kernel(const DeltaArgs a, int n_scan, int cols_per_block) {
   constexpr int DKP = 4 * KPL;
   extern __shared__ float4 smem4[];
   float* smem = reinterpret_cast<float*>(smem4);
@@ -67,8 +71,9 @@ __global__ void delta_scan_kernel(const DeltaArgs a, int n_scan) {
   pdl_wait();
   const int h = blockIdx.x, req = blockIdx.y;
   const int Dk = a.Dk, Dv = a.Dv;
-  const int dvp = (Dv + 3) & ~3;
-  const int tok_floats = 5 * DKP + 2 * dvp + 4;      // d, p, x, k, y | c | o | (p.r, k.r)
+  const int dvp = cols_per_block;                     // columns of this block (a multiple of 8), from col0 on
+  const int col0 = blockIdx.z * cols_per_block;
+  const int tok_floats = 5 * DKP + dvp + 4;           // d, p, x, k, y | c | (p.r, k.r)
   const int buf_floats = kChunk * tok_floats;
   const int t0 = a.q_start[req], t1 = a.q_start[req + 1];
   const int lane = threadIdx.x & 31;
@@ -77,15 +82,15 @@ __global__ void delta_scan_kernel(const DeltaArgs a, int n_scan) {
   const bool scanner = (int)threadIdx.x < n_scan;
   const int n_help = (int)blockDim.x - n_scan;
   const bool piped = n_help > 0;
-  const int col = threadIdx.x >> 2, part = threadIdx.x & 3;
+  const int lcol = threadIdx.x >> 2, part = threadIdx.x & 3;     // column inside the block's share
+  const int col = col0 + lcol;
+  const bool owns = lcol < dvp && col < Dv;
   const int hk = h / (a.H / a.G);
   const T* rp = static_cast<const T*>(a.r);
   const T* kp = static_cast<const T*>(a.k);
   const T* vp = static_cast<const T*>(a.v);
-  const T* gp = static_cast<const T*>(a.gate);
   const T* dp = static_cast<const T*>(a.decay);
   const T* xp = static_cast<const T*>(a.aux);
-  T* outp = static_cast<T*>(a.out);
 
   float s[KPL];
   float* my_state = a.state + (size_t)a.slots[req] * a.slot_stride + ((size_t)h * Dv + col) * DKP;
@@ -93,7 +98,7 @@ __global__ void delta_scan_kernel(const DeltaArgs a, int n_scan) {
 #pragma unroll
   for (int e4 = 0; e4 < KPL / 4; ++e4) {
     float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (scanner && !fresh && col < Dv) v4 = *reinterpret_cast<const float4*>(my_state + (e4 * 4 + part) * 4);
+    if (scanner && !fresh && owns) v4 = *reinterpret_cast<const float4*>(my_state + (e4 * 4 + part) * 4);
     s[e4 * 4 + 0] = v4.x; s[e4 * 4 + 1] = v4.y; s[e4 * 4 + 2] = v4.z; s[e4 * 4 + 3] = v4.w;
   }
   const float rate = MODE == MODE_GATED ? expf(a.head_rate[h]) : 0.60653065971263342f;   // e^{-1/2}
@@ -107,6 +112,13 @@ __global__ void delta_scan_kernel(const DeltaArgs a, int n_scan) {
       constexpr int U = (DKP + 31) / 32;
       float kr_[U], rr_[U], zd_[U], za_[U];
       float ksum = 0.f, rsum = 0.f;
+      // the token's column values c_j are requested with everything else (up to 256 columns: 8 per lane)
+      float cv_[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int j = u * 32 + lane;
+        cv_[u] = (j < dvp && col0 + j < Dv) ? to_f32(vp[(size_t)t * a.ld_v + h * Dv + col0 + j]) : 0.f;
+      }
 #pragma unroll
       for (int u = 0; u < U; ++u) {                 // every load of the token is under way before the first sum
         const int i = u * 32 + lane;
@@ -151,26 +163,20 @@ __global__ void delta_scan_kernel(const DeltaArgs a, int n_scan) {
       pr = warp_sum(pr);
       kr = warp_sum(kr);
       if (MODE == MODE_GATED) pr = beta * kr;
-      if (lane == 0) { tok[5 * DKP + 2 * dvp] = pr; tok[5 * DKP + 2 * dvp + 1] = kr; }
-    }
-    // the chunk's column values c_j
-    for (int idx = th0; idx < n * dvp; idx += nth) {
-      const int c = idx / dvp, j = idx - c * dvp;
-      const int t = base + c;
-      float cv = 0.f;
-      if (j < Dv) {
-        cv = to_f32(vp[(size_t)t * a.ld_v + h * Dv + j]);
-        if (MODE == MODE_GATED) cv *= sigmoidf_(to_f32(xp[(size_t)t * a.ld_aux + h]));
+      if (lane == 0) { tok[5 * DKP + dvp] = pr; tok[5 * DKP + dvp + 1] = kr; }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int j = u * 32 + lane;
+        if (j < dvp) tok[5 * DKP + j] = MODE == MODE_GATED ? beta * cv_[u] : cv_[u];
       }
-      buf[(size_t)c * tok_floats + 5 * DKP + j] = cv;
     }
   };
 
   // ---- the scan over a chunk.  Every scanning thread takes part (the shuffles name the whole
   // warp); threads beyond the last column carry zeros and store nothing.
-  auto scan = [&](int n, float* buf) {
+  auto scan = [&](int base, int n, const float* buf) {
     for (int c = 0; c < n; ++c) {
-      float* tok = buf + (size_t)c * tok_floats;
+      const float* tok = buf + (size_t)c * tok_floats;
       const float4* D4 = reinterpret_cast<const float4*>(tok);
       const float4* P4 = reinterpret_cast<const float4*>(tok + DKP);
       const float4* X4 = reinterpret_cast<const float4*>(tok + 2 * DKP);
@@ -189,9 +195,9 @@ __global__ void delta_scan_kernel(const DeltaArgs a, int n_scan) {
       float dx = (dx0 + dx1) + (dx2 + dx3), dy = (dy0 + dy1) + (dy2 + dy3);
       dx += __shfl_xor_sync(0xffffffffu, dx, 1); dy += __shfl_xor_sync(0xffffffffu, dy, 1);
       dx += __shfl_xor_sync(0xffffffffu, dx, 2); dy += __shfl_xor_sync(0xffffffffu, dy, 2);
-      const float cj = col < dvp ? tok[5 * DKP + col] : 0.f;
-      const float pr = tok[5 * DKP + 2 * dvp], kr = tok[5 * DKP + 2 * dvp + 1];
-      if (part == 0 && col < dvp) tok[5 * DKP + dvp + col] = dy - dx * pr + cj * kr;
+      const float cj = lcol < dvp ? tok[5 * DKP + lcol] : 0.f;
+      const float pr = tok[5 * DKP + dvp], kr = tok[5 * DKP + dvp + 1];
+      if (part == 0 && owns) a.o_raw[(size_t)(base + c) * a.H * Dv + h * Dv + col] = dy - dx * pr + cj * kr;
 #pragma unroll
       for (int e4 = 0; e4 < KPL / 4; ++e4) {
         const float4 dv = D4[e4 * 4 + part], pv = P4[e4 * 4 + part], kv = K4[e4 * 4 + part];
@@ -203,60 +209,33 @@ __global__ void delta_scan_kernel(const DeltaArgs a, int n_scan) {
     }
   };
 
-  // ---- a chunk's outputs: RMS over the head, weight, sigmoid gate; one warp per token
-  auto finish = [&](int base, int n, const float* buf, int w0, int nw) {
-    for (int c = w0; c < n; c += nw) {
-      const int t = base + c;
-      const float* o = buf + (size_t)c * tok_floats + 5 * DKP + dvp;
-      float ss = 0.f;
-      for (int j = lane; j < Dv; j += 32) ss += o[j] * o[j];
-      ss = warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss / (float)Dv + a.eps);
-      for (int j = lane; j < Dv; j += 32) {
-        const float w = a.norm_w[(a.norm_per_head ? h * Dv : 0) + j];
-        const float g = sigmoidf_(to_f32(gp[(size_t)t * a.ld_gate + h * Dv + j]));
-        outp[(size_t)t * a.ld_out + h * Dv + j] = from_f32<T>(o[j] * inv * w * g);
-      }
-    }
-  };
-
   if (!piped) {
-    // one group of threads does the three phases in turn
+    // one group of threads prepares and scans in turn
     const int warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     for (int base = t0; base < t1; base += kChunk) {
       const int n = min(kChunk, t1 - base);
       prepare(base, n, smem, warp, nwarps, threadIdx.x, blockDim.x);
       __syncthreads();
-      scan(n, smem);
-      __syncthreads();
-      finish(base, n, smem, warp, nwarps);
+      scan(base, n, smem);
       __syncthreads();
     }
   } else {
-    // Two buffers.  In round i the scanning threads walk chunk i while the helpers finish chunk
-    // i - 1 (they read only its outputs, which nobody writes in this round) and prepare chunk
-    // i + 1 in the same buffer (everything but the outputs, which chunk i - 1's scan is done with).
+    // Two buffers: in round i the scanning threads walk chunk i while the helpers prepare chunk i + 1.
     const int n_chunks = (t1 - t0 + kChunk - 1) / kChunk;
     const int hw = ((int)threadIdx.x - n_scan) >> 5, hnw = n_help >> 5, hth = (int)threadIdx.x - n_scan;
     if (!scanner && n_chunks > 0) prepare(t0, min(kChunk, t1 - t0), smem, hw, hnw, hth, n_help);
     __syncthreads();
-    for (int i = 0; i <= n_chunks; ++i) {
+    for (int i = 0; i < n_chunks; ++i) {
+      const int base = t0 + i * kChunk;
       if (scanner) {
-        if (i < n_chunks) scan(min(kChunk, t1 - (t0 + i * kChunk)), smem + (size_t)(i & 1) * buf_floats);
-      } else {
-        if (i >= 1) {
-          const int base = t0 + (i - 1) * kChunk;
-          finish(base, min(kChunk, t1 - base), smem + (size_t)((i - 1) & 1) * buf_floats, hw, hnw);
-        }
-        if (i + 1 < n_chunks) {
-          const int base = t0 + (i + 1) * kChunk;
-          prepare(base, min(kChunk, t1 - base), smem + (size_t)((i + 1) & 1) * buf_floats, hw, hnw, hth, n_help);
-        }
+        scan(base, min(kChunk, t1 - base), smem + (size_t)(i & 1) * buf_floats);
+      } else if (i + 1 < n_chunks) {
+        prepare(base + kChunk, min(kChunk, t1 - base - kChunk), smem + (size_t)((i + 1) & 1) * buf_floats, hw, hnw, hth, n_help);
       }
       __syncthreads();
     }
   }
-  if (scanner && col < Dv) {
+  if (scanner && owns) {
 #pragma unroll
     for (int e4 = 0; e4 < KPL / 4; ++e4)
       *reinterpret_cast<float4*>(my_state + (e4 * 4 + part) * 4) =
@@ -274,11 +253,38 @@ static int delta_kpl(int Dk) {
 
 KVB_EXPORT int kvb_delta_key_pad(int Dk) { return Dk >= 1 ? 4 * delta_kpl(Dk) : 0; }
 
+// The read-outs' norm and gate: out[t, h, :] = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate), one warp per (token, head).
+template <typename T>
+__global__ void delta_finish_kernel(const DeltaArgs a, int T_) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= (long long)T_ * a.H) return;
+  const int t = (int)(unit / a.H), h = (int)(unit - (long long)t * a.H);
+  const int Dv = a.Dv;
+  const float* o = a.o_raw + (size_t)t * a.H * Dv + h * Dv;
+  const T* gp = static_cast<const T*>(a.gate) + (size_t)t * a.ld_gate + h * Dv;
+  T* outp = static_cast<T*>(a.out) + (size_t)t * a.ld_out + h * Dv;
+  float ss = 0.f;
+  for (int j = lane; j < Dv; j += 32) ss += o[j] * o[j];
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)Dv + a.eps);
+  for (int j = lane; j < Dv; j += 32) {
+    const float w = a.norm_w[(a.norm_per_head ? h * Dv : 0) + j];
+    outp[j] = from_f32<T>(o[j] * inv * w * sigmoidf_(to_f32(gp[j])));
+  }
+}
+
 template <typename T, int KPL, int MODE>
-static int launch_scan(const DeltaArgs& a, int R, int max_run, cudaStream_t stream) {
-  const int dvp = (a.Dv + 3) & ~3;
-  const int n_scan = ((4 * dvp + 31) / 32) * 32;
-  // up to sixteen warps beside the scanning ones, so that a chunk's sixteen tokens are prepared at once
+static int launch_scan(const DeltaArgs& a, int R, int T_, int max_run, cudaStream_t stream) {
+  const int dv8 = (a.Dv + 7) & ~7;
+  // A head's columns are shared out over several blocks while the grid would otherwise leave SMs idle (one
+  // long prompt alone); shares are multiples of 8 columns.  The results do not depend on the split.
+  int split = 1;
+  while ((long long)a.H * R * split < kvb_sm_count() && dv8 / (split * 2) >= 8 && (dv8 / (split * 2)) % 8 == 0) split *= 2;
+  const int cols = dv8 / split;
+  const int n_scan = 4 * cols;
   static int max_threads = 0;                 // what the kernel's registers allow in one block
   if (max_threads == 0) {
     cudaFuncAttributes attr;
@@ -287,27 +293,30 @@ static int launch_scan(const DeltaArgs& a, int R, int max_run, cudaStream_t stre
     max_threads = attr.maxThreadsPerBlock / 32 * 32;
   }
   if (n_scan > max_threads) return KVB_ERR_BAD_SIZE;
+  // up to sixteen warps beside the scanning ones prepare the next chunk (one token each) meanwhile
   int n_help = max_threads - n_scan < 512 ? max_threads - n_scan : 512;
   if (n_help < 128) n_help = 0;               // too few to keep up: the scanning threads do everything in turn
   if (max_run > 0 && max_run <= kChunk) n_help = 0;   // a single chunk per request (decode steps): nothing to overlap
-  const size_t buf = (size_t)kChunk * (5 * 4 * KPL + 2 * dvp + 4) * sizeof(float);
+  const size_t buf = (size_t)kChunk * (5 * 4 * KPL + cols + 4) * sizeof(float);
   const size_t smem = n_help ? 2 * buf : buf;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<T, KPL, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  kvb_launch(delta_scan_kernel<T, KPL, MODE>, dim3(a.H, R), dim3(n_scan + n_help), smem, stream, a, n_scan);
+  kvb_launch(delta_scan_kernel<T, KPL, MODE>, dim3(a.H, R, split), dim3(n_scan + n_help), smem, stream, a, n_scan, cols);
+  const long long units = (long long)T_ * a.H;
+  kvb_launch(delta_finish_kernel<T>, dim3((unsigned)((units + 7) / 8)), dim3(256), 0, stream, a, T_);
   return kvb_launch_result();
 }
 
 template <typename T, int MODE>
-static int launch_scan_kpl(const DeltaArgs& a, int R, int max_run, cudaStream_t stream) {
+static int launch_scan_kpl(const DeltaArgs& a, int R, int T_, int max_run, cudaStream_t stream) {
   switch (delta_kpl(a.Dk)) {
-    case 4: return launch_scan<T, 4, MODE>(a, R, max_run, stream);
-    case 8: return launch_scan<T, 8, MODE>(a, R, max_run, stream);
-    case 16: return launch_scan<T, 16, MODE>(a, R, max_run, stream);
-    case 32: return launch_scan<T, 32, MODE>(a, R, max_run, stream);
+    case 4: return launch_scan<T, 4, MODE>(a, R, T_, max_run, stream);
+    case 8: return launch_scan<T, 8, MODE>(a, R, T_, max_run, stream);
+    case 16: return launch_scan<T, 16, MODE>(a, R, T_, max_run, stream);
+    case 32: return launch_scan<T, 32, MODE>(a, R, T_, max_run, stream);
   }
   return KVB_ERR_BAD_SIZE;
 }
@@ -315,16 +324,17 @@ static int launch_scan_kpl(const DeltaArgs& a, int R, int max_run, cudaStream_t 
 // max_run: the longest run of tokens among the requests if the host knows it (0: unknown); the
 // results do not depend on it.  Refuses: Dk > 128, Dv > 256, Dv > 128 together with Dk > 64 (a
 // thread's quarter column would not stay in registers), heads that do not group evenly.
-KVB_EXPORT int kvb_delta_scan(const DeltaArgs* args, int mode, int R, int max_run, int dtype, cudaStream_t stream) {
+KVB_EXPORT int kvb_delta_scan(const DeltaArgs* args, int mode, int R, int T_, int max_run, int dtype, cudaStream_t stream) {
   const DeltaArgs& a = *args;
-  if (R <= 0) return 0;
+  if (R <= 0 || T_ <= 0) return 0;
+  if (a.o_raw == nullptr) return KVB_ERR_BAD_SIZE;
   if (a.Dk < 1 || a.Dk > 128 || a.Dv < 1 || a.Dv > 256 || (a.Dk > 64 && a.Dv > 128)) return KVB_ERR_BAD_SIZE;
   if (a.G < 1 || a.H % a.G || R > 65535) return KVB_ERR_BAD_SIZE;
   if (mode != MODE_GENERAL && mode != MODE_GATED) return KVB_ERR_BAD_SIZE;
   if (mode == MODE_GENERAL) {
-    KVB_DISPATCH_DTYPE(dtype, T, return (launch_scan_kpl<T, MODE_GENERAL>(a, R, max_run, stream)));
+    KVB_DISPATCH_DTYPE(dtype, T, return (launch_scan_kpl<T, MODE_GENERAL>(a, R, T_, max_run, stream)));
   } else {
-    KVB_DISPATCH_DTYPE(dtype, T, return (launch_scan_kpl<T, MODE_GATED>(a, R, max_run, stream)));
+    KVB_DISPATCH_DTYPE(dtype, T, return (launch_scan_kpl<T, MODE_GATED>(a, R, T_, max_run, stream)));
   }
   return KVB_ERR_BAD_DTYPE;
 }

@@ -373,14 +373,14 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_abs, int ld_qa, i
   extern __shared__ uint4 tc_smem4[];
   const int Dc = rank + rot, DcP = Dc + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(tc_smem4);              // [64][DcP]
-  __nv_bfloat16* Ks = Qs + TC_ROWS * DcP;                                       // [32][DcP]
-  __nv_bfloat16* Ps = Ks + TC_KEYS * DcP;                                       // [64][TC_PPAD]
+  __nv_bfloat16* Ks0 = Qs + TC_ROWS * DcP;                                      // two buffers of [32][DcP]
+  __nv_bfloat16* Ps = Ks0 + 2 * TC_KEYS * DcP;                                  // [64][TC_PPAD]
   float* Ss = reinterpret_cast<float*>(Ps + TC_ROWS * TC_PPAD);                 // [64][TC_SPAD]
   float* m_s = Ss + TC_ROWS * TC_SPAD;
   float* l_s = m_s + TC_ROWS;
   float* corr_s = l_s + TC_ROWS;
   int* pos_s = reinterpret_cast<int*>(corr_s + TC_ROWS);
-  __shared__ long long row_of[TC_KEYS];
+  __shared__ int row_ok[2][TC_KEYS];              // per buffer: whether the key's row could be read
 
   pdl_trigger();
   pdl_wait();
@@ -435,31 +435,45 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_abs, int ld_qa, i
 #pragma unroll
   for (int n = 0; n < NT; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
 
-  for (int c0 = 0; c0 <= max_pos; c0 += TC_KEYS) {
-    const int n_keys = min(TC_KEYS, max_pos - c0 + 1);
-    __syncthreads();                               // the chunk before is used up (first round: Qs and the row state are written)
-    if (tid < TC_KEYS) {
-      long long off = -1;
-      if (tid < n_keys) {
-        const int j = c0 + tid;
-        const int lp = j / page_size;
-        const int page = lp < max_pages ? table[lp] : -1;
-        if (page < 0 || page >= num_pages) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
-        else off = ((long long)page * page_size + (j % page_size)) * Dc;
-      }
-      row_of[tid] = off;
-    }
-    __syncthreads();
-    const int vecs = Dc >> 3;                      // 16-byte pieces per row
+  // A chunk's rows are requested (cp.async, 16 bytes a piece) one chunk ahead, into the other buffer.
+  const int vecs = Dc >> 3;                        // 16-byte pieces per row
+  auto request_chunk = [&](int c0, int buf) {
+    __nv_bfloat16* Kb = Ks0 + (size_t)buf * TC_KEYS * DcP;
     for (int j = warp; j < TC_KEYS; j += TC_THREADS / 32) {
-      const long long off = row_of[j];
-      uint4* dst = reinterpret_cast<uint4*>(Ks + (size_t)j * DcP);
-      const uint4* src = reinterpret_cast<const uint4*>(pages + (off >= 0 ? off : 0));
-      for (int v = lane; v < vecs; v += 32) dst[v] = off >= 0 ? src[v] : make_uint4(0u, 0u, 0u, 0u);
+      const int key = c0 + j;
+      long long off = -1;
+      if (key <= max_pos) {
+        const int lp = key / page_size;
+        const int page = lp < max_pages ? table[lp] : -1;
+        if (page < 0 || page >= num_pages) { if (lane == 0) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE); }
+        else off = ((long long)page * page_size + (key % page_size)) * Dc;
+      }
+      if (lane == 0) row_ok[buf][j] = off >= 0;
+      __nv_bfloat16* dst = Kb + (size_t)j * DcP;
+      if (off >= 0) {
+        const __nv_bfloat16* src = pages + off;
+        for (int v = lane; v < vecs; v += 32) {
+          const unsigned d = (unsigned)__cvta_generic_to_shared(dst + 8 * v);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(d), "l"(src + 8 * v) : "memory");
+        }
+      } else {
+        for (int v = lane; v < vecs; v += 32) reinterpret_cast<uint4*>(dst)[v] = make_uint4(0u, 0u, 0u, 0u);
+      }
     }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (max_pos >= 0) request_chunk(0, 0);
+  const bool row_group_live = mrow < rows_used;   // a warp whose 16 rows are all empty only keeps the barriers
+  int it = 0;
+  for (int c0 = 0; c0 <= max_pos; c0 += TC_KEYS, ++it) {
+    const int n_keys = min(TC_KEYS, max_pos - c0 + 1);
+    const __nv_bfloat16* Ks = Ks0 + (size_t)(it & 1) * TC_KEYS * DcP;
+    const int* ok = row_ok[it & 1];
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                               // this chunk has arrived; the chunk before is used up (first round: Qs and the row state are written)
+    if (c0 + TC_KEYS <= max_pos) request_chunk(c0 + TC_KEYS, (it + 1) & 1);
     // ---- scores: this warp's 16 rows against 16 of the chunk's keys
-    {
+    if (row_group_live) {
       const int kcol = (warp >> 2) * 16;
       float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
       const __nv_bfloat16* a_ptr = Qs + (size_t)(mrow + (lane & 15)) * DcP + (lane >> 4) * 8;
@@ -485,7 +499,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_abs, int ld_qa, i
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const int kk = k0 + e;
-        const bool valid = kk < n_keys && c0 + kk <= pos_r && row_of[kk] >= 0;
+        const bool valid = kk < n_keys && c0 + kk <= pos_r && ok[kk];
         sv[e] = valid ? Ss[(size_t)row * TC_SPAD + kk] : -CUDART_INF_F;
         mx = fmaxf(mx, sv[e]);
       }
@@ -512,7 +526,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_abs, int ld_qa, i
     }
     __syncthreads();
     // ---- O = O * corr + P V for this warp's 16 rows and its half of the value columns
-    {
+    if (row_group_live) {
       const float c_lo = corr_s[mrow + g], c_hi = corr_s[mrow + g + 8];
 #pragma unroll
       for (int n = 0; n < NT; ++n) { acc[n][0] *= c_lo; acc[n][1] *= c_lo; acc[n][2] *= c_hi; acc[n][3] *= c_hi; }
@@ -567,7 +581,7 @@ static int launch_latent_tc(const void* q_abs, int ld_qa, int hs_qa, const void*
                             const int* q_start, const int* tiles, int n_tiles, const float* sink, float scale, void* out,
                             int ld_out, int hs_out, int H, int rank, int rot, int* status, cudaStream_t stream) {
   const int DcP = rank + rot + 8;
-  const size_t smem = (size_t)(TC_ROWS + TC_KEYS) * DcP * 2 + (size_t)TC_ROWS * TC_PPAD * 2 +
+  const size_t smem = (size_t)(TC_ROWS + 2 * TC_KEYS) * DcP * 2 + (size_t)TC_ROWS * TC_PPAD * 2 +
                       (size_t)TC_ROWS * TC_SPAD * 4 + 4 * TC_ROWS * 4;
   if (smem > 220 * 1024) return KVB_ERR_BAD_SIZE;
   if (smem > 48 * 1024) {

@@ -130,10 +130,48 @@ __global__ void bias_act_mul_kernel(const T* __restrict__ gu, const float* __res
   }
 }
 
+// bfloat16 rows whose halves are multiples of 8 wide: eight elements per thread, 16-byte accesses.
+__global__ void bias_act_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ bias,
+                                           __nv_bfloat16* __restrict__ out, int I, int kind, size_t groups) {
+  pdl_trigger();
+  pdl_wait();
+  const int gpr = I >> 3;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / gpr;
+    const int i = (int)(idx - t * gpr) << 3;
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + t * 2 * I + i);
+    const uint4 u = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + i);
+    const unsigned gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    unsigned ow[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xffff0000u);
+      float u0 = __uint_as_float(uw[k] << 16), u1 = __uint_as_float(uw[k] & 0xffff0000u);
+      if (bias) {
+        g0 += bias[i + 2 * k]; g1 += bias[i + 2 * k + 1];
+        u0 += bias[I + i + 2 * k]; u1 += bias[I + i + 2 * k + 1];
+      }
+      __nv_bfloat162 v = __floats2bfloat162_rn(act_apply(g0, kind) * u0, act_apply(g1, kind) * u1);
+      ow[k] = *reinterpret_cast<unsigned*>(&v);
+    }
+    *reinterpret_cast<uint4*>(out + t * I + i) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+}
+
 KVB_EXPORT int kvb_bias_act_mul(const void* gu, const float* bias, void* out, int T_, int I, int kind, int dtype,
                                 cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (I < 1 || kind < 0 || kind > 1) return KVB_ERR_BAD_SIZE;
+  if (dtype == KVB_BF16 && I % 8 == 0 && (reinterpret_cast<uintptr_t>(gu) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    const size_t groups = (size_t)T_ * (I / 8);
+    const size_t want8 = (groups + 255) / 256;
+    const int blocks8 = (int)(want8 < (size_t)kvb_sm_count() * 16 ? want8 : (size_t)kvb_sm_count() * 16);
+    kvb_launch(bias_act_mul_bf16x8_kernel, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)gu, bias,
+               (__nv_bfloat16*)out, I, kind, groups);
+    return kvb_launch_result();
+  }
   const size_t total = (size_t)T_ * I;
   const size_t want = (total + 255) / 256;
   const int blocks = (int)(want < (size_t)kvb_sm_count() * 16 ? want : (size_t)kvb_sm_count() * 16);

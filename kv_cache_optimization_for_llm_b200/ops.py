@@ -355,7 +355,7 @@ class _DeltaArgs(ctypes.Structure):
                 ("head_rate", c_void_p), ("norm_w", c_void_p), ("norm_per_head", c_int), ("state", c_void_p),
                 ("slot_stride", c_longlong), ("out", c_void_p), ("ld_out", c_int), ("q_start", c_void_p),
                 ("req_start", c_void_p), ("slots", c_void_p), ("H", c_int), ("G", c_int), ("Dk", c_int), ("Dv", c_int),
-                ("eps", c_float)]
+                ("eps", c_float), ("o_raw", c_void_p)]
 
 
 _key_pad: Dict[int, int] = {}
@@ -399,10 +399,13 @@ def delta_scan(mode: str, batch, state: torch.Tensor, r, k, v, gate, decay, aux,
     a.out, a.ld_out = out.data_ptr(), out.stride(0)
     a.q_start, a.req_start, a.slots = batch.q_start.data_ptr(), batch.req_start.data_ptr(), batch.slots.data_ptr()
     a.H, a.G, a.Dk, a.Dv, a.eps = heads, key_heads, dk, dv, eps
+    a.o_raw = new((T, heads * dv), torch.float32, x0.device).data_ptr()
     rc = lib("delta_rule").kvb_delta_scan(ctypes.byref(a), c_int({"general": 0, "gated": 1}[mode]),
-                                          c_int(batch.num_reqs), c_int(int(getattr(batch, "max_q_len", 0) or 0)),
+                                          c_int(batch.num_reqs), c_int(T), c_int(int(getattr(batch, "max_q_len", 0) or 0)),
                                           c_int(dtype_code(x0.dtype)), _stream())
     _check(rc, "delta_scan")
+    global launch_count
+    launch_count += 1       # the scan and the read-outs' norm
     choices["delta_scan_" + mode] += 1
     return out
 

@@ -82,7 +82,7 @@ class GeneralDelta(Part):
 
     def activation_widths(self):
         hd = self.heads * self.dim
-        return [self.w_in.shape[0], _pad8(self.lr), hd, hd, self.o.shape[0]]
+        return [self.w_in.shape[0], _pad8(self.lr), hd, 3 * hd, self.o.shape[0]]      # 3 hd: the read-outs in float32, and normed
 
     def forward(self, x, batch, cache):
         p = ops.linear(x, self.w_in)
@@ -153,7 +153,7 @@ class ChannelDelta(Part):
 
     def activation_widths(self):
         hv = self.heads * self.vdim
-        return [self.w_in.shape[0], self.channels, self.heads * self.dim, hv, hv, self.o.shape[0]]
+        return [self.w_in.shape[0], self.channels, self.heads * self.dim, hv, 3 * hv, self.o.shape[0]]
 
     def forward(self, x, batch, cache):
         p = ops.linear(x, self.w_in)
