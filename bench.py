@@ -430,10 +430,15 @@ def llama_config_like(z):
     return cfg
 
 
+_compare_windows = []      # wall-clock intervals of the timed repetitions, for the clock samples
+
+
 def _time_steps(fn, reps, warmup):
     import torch
     times = []
     for k in range(warmup + reps):
+        if k == warmup:
+            t_first = time.perf_counter()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         start.record()
@@ -442,6 +447,7 @@ def _time_steps(fn, reps, warmup):
         torch.cuda.synchronize()
         if k >= warmup:
             times.append(start.elapsed_time(stop))
+    _compare_windows.append((t_first, time.perf_counter()))
     return statistics.median(times)
 
 
@@ -516,9 +522,13 @@ def run_compare(size):
     H, Dk = z["heads"], 64
     dc = z["kv_rank"] + z["lat_rot"]
 
-    def per_launch(d, phase, key, name):
-        n, ms = d[phase][key].get(name, (0, 0.0))
-        return ms / n if n else None
+    def per_launch(d, phase, key, *names):
+        """Milliseconds per call of the operator (the first of ``names`` that the step used)."""
+        for name in names:
+            n, ms = d[phase][key].get(name, (0, 0.0))
+            if n:
+                return ms / n
+        return None
 
     def frac(work, ms, peak_per_s):
         return None if not ms else round(work / (ms * 1e-3) / peak_per_s, 4)
@@ -527,15 +537,16 @@ def run_compare(size):
         # prefill: FLOPs of the kernel's own arithmetic over the time of one launch
         "llama flash_attention, 2048 tokens (of the measured bf16 peak)": frac(
             pairs * 4 * z["heads"] * 64, per_launch(llama, "prefill_2048", "operators", "paged_flash_attention"), tensor),
-        "rezusun latent_attention, 2048 tokens (of the nominal fp32 FMA peak)": frac(
-            pairs * z["lat_heads"] * 2 * (dc + z["kv_rank"]), per_launch(rez, "prefill_2048", "operators", "latent_attention"), fma),
+        "rezusun latent_attention, 2048 tokens (of the measured bf16 peak)": frac(
+            pairs * z["lat_heads"] * 2 * (dc + z["kv_rank"]),
+            per_launch(rez, "prefill_2048", "operators", "latent_attention_tc", "latent_attention"), tensor),
         "rezusun delta_scan, 2048 tokens (of the nominal fp32 FMA peak)": frac(
             T * H * Dk * 64 * 10, per_launch(rez, "prefill_2048", "operators", "delta_scan"), fma),
         # decode, 64 requests at 512 tokens: bytes that must move over the time of one launch
         "llama decode_attention_mma, batch 64 (of the measured copy peak)": frac(
             R * ctx * 2 * (z["heads"] // 4) * 64 * 2, per_launch(llama, "decode_b64", "operators_launched", "decode_attention_mma"), hbm),
         "rezusun latent_attention, batch 64 (of the measured copy peak)": frac(
-            R * ctx * dc * 2, per_launch(rez, "decode_b64", "operators_launched", "latent_attention"), hbm),
+            R * ctx * dc * 2, per_launch(rez, "decode_b64", "operators_launched", "latent_attention_tc", "latent_attention"), hbm),
         "rezusun delta_scan, batch 64 (of the measured copy peak)": frac(
             2 * R * H * 64 * Dk * 4, per_launch(rez, "decode_b64", "operators_launched", "delta_scan"), hbm),
         "llama add_rmsnorm, 2048 tokens (of the measured copy peak)": frac(
@@ -545,7 +556,7 @@ def run_compare(size):
     }
     return {"compare": size, "sizes": z, "dtype": "bf16", "data": "synthetic", "peaks": pk, "llama": llama, "rezusun": rez,
             "kernel_roofline_fractions": kernels, "layers_of_each_kind": n_each,
-            "clocks": sampler.summary([(w0, w1)])}
+            "clocks": sampler.summary(list(_compare_windows) or [(w0, w1)])}
 
 
 def main():

@@ -20,7 +20,7 @@
 // one (head, request): it walks the request's tokens of this step in chunks of 16.  A chunk is
 // prepared (its projections become the float32 vectors above, one warp per token) and scanned
 // (the threads that own the columns step through it and leave the read-outs in a float32
-// scratch); up to sixteen more warps prepare chunk i + 1 while the scan walks chunk i, in two
+// scratch); up to eight more warps prepare chunk i + 1 while the scan walks chunk i, in two
 // buffers, one block barrier per chunk.  A second small kernel norms each head's read-out (RMS,
 // weight, sigmoid gate).  The scan is bound by shared memory: every column re-reads the token's
 // five vectors, which is why a head's columns are spread over several SMs when there is room.  The state is read from the request's
@@ -293,8 +293,10 @@ static int launch_scan(const DeltaArgs& a, int R, int T_, int max_run, cudaStrea
     max_threads = attr.maxThreadsPerBlock / 32 * 32;
   }
   if (n_scan > max_threads) return KVB_ERR_BAD_SIZE;
-  // up to sixteen warps beside the scanning ones prepare the next chunk (one token each) meanwhile
-  int n_help = max_threads - n_scan < 512 ? max_threads - n_scan : 512;
+  // Up to eight warps beside the scanning ones prepare the next chunk (two tokens each) meanwhile.  Sixteen
+  // were measured slower by half: the scan is a chain of dependent steps in two to eight warps, and every
+  // further warp on the SM takes issue slots from them.
+  int n_help = max_threads - n_scan < 256 ? max_threads - n_scan : 256;
   if (n_help < 128) n_help = 0;               // too few to keep up: the scanning threads do everything in turn
   if (max_run > 0 && max_run <= kChunk) n_help = 0;   // a single chunk per request (decode steps): nothing to overlap
   const size_t buf = (size_t)kChunk * (5 * 4 * KPL + cols + 4) * sizeof(float);

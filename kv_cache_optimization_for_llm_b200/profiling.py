@@ -100,7 +100,7 @@ def main(argv=None) -> int:
         torch.cuda.synchronize()
         ms = (time.perf_counter() - t0) * 1e3
         prof.cudaProfilerStop()
-        print(f"prefill of {a.tokens} tokens, {cfg['num_hidden_layers']} layers: {ms:.3f} ms")
+        print(f"prefill of {a.tokens} tokens, {len(eng.runner.spec.schedule)} layer runs: {ms:.3f} ms")
         return 0
     sp = SamplingParams(max_tokens=48 + a.steps, ignore_eos=True)
     ids = [eng.add_request(rng.integers(0, vocab, a.prompt).tolist(), sp) for _ in range(a.batch)]
@@ -119,7 +119,7 @@ def main(argv=None) -> int:
     torch.cuda.synchronize()
     ms = (time.perf_counter() - t0) * 1e3 / a.steps
     prof.cudaProfilerStop()
-    print(f"decode, batch {a.batch}, {cfg['num_hidden_layers']} layers: {ms:.3f} ms per step")
+    print(f"decode, batch {a.batch}, {len(eng.runner.spec.schedule)} layer runs: {ms:.3f} ms per step")
     return 0
 
 
