@@ -478,13 +478,30 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_abs, int ld_qa, i
       float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
       const __nv_bfloat16* a_ptr = Qs + (size_t)(mrow + (lane & 15)) * DcP + (lane >> 4) * 8;
       const __nv_bfloat16* b_ptr = Ks + (size_t)(kcol + ((lane >> 4) << 3) + (lane & 7)) * DcP + ((lane >> 3) & 1) * 8;
-      for (int ks = 0; ks < Dc; ks += 16) {
+      // two sets of sums, for the even and the odd steps along Dc: four chains of dependent products instead
+      // of two, and the operands of a pair of steps are fetched together (the same order for every row)
+      float u0[4] = {0.f, 0.f, 0.f, 0.f}, u1[4] = {0.f, 0.f, 0.f, 0.f};
+      int ks = 0;
+      for (; ks + 32 <= Dc; ks += 32) {
+        unsigned a0, a1, a2, a3, b0, b1, b2, b3, c0_, c1_, c2_, c3_, d0, d1, d2, d3;
+        ldsm_x4(a0, a1, a2, a3, a_ptr + ks);
+        ldsm_x4(b0, b1, b2, b3, b_ptr + ks);
+        ldsm_x4(c0_, c1_, c2_, c3_, a_ptr + ks + 16);
+        ldsm_x4(d0, d1, d2, d3, b_ptr + ks + 16);
+        mma_bf16_16816(s0, a0, a1, a2, a3, b0, b1);
+        mma_bf16_16816(s1, a0, a1, a2, a3, b2, b3);
+        mma_bf16_16816(u0, c0_, c1_, c2_, c3_, d0, d1);
+        mma_bf16_16816(u1, c0_, c1_, c2_, c3_, d2, d3);
+      }
+      if (ks < Dc) {
         unsigned a0, a1, a2, a3, b0, b1, b2, b3;
         ldsm_x4(a0, a1, a2, a3, a_ptr + ks);
         ldsm_x4(b0, b1, b2, b3, b_ptr + ks);
         mma_bf16_16816(s0, a0, a1, a2, a3, b0, b1);
         mma_bf16_16816(s1, a0, a1, a2, a3, b2, b3);
       }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { s0[e] += u0[e]; s1[e] += u1[e]; }
       float* srow = Ss + (size_t)(mrow + g) * TC_SPAD + kcol + 2 * t4;
       srow[0] = s0[0] * scale; srow[1] = s0[1] * scale; srow[8] = s1[0] * scale; srow[9] = s1[1] * scale;
       srow += 8 * TC_SPAD;
