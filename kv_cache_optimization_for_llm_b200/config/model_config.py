@@ -192,7 +192,7 @@ class RezusunLayerConfig:
 
 
 _REZUSUN_MIXER_KEYS = {
-    "latent_attention": ("heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank", "scale", "rot"),
+    "latent_attention": ("heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank", "rot"),   # "scale" may be left out
     "general_delta": ("heads", "dim"),
     "channel_delta": ("heads", "kv_heads", "dim", "vdim", "conv"),
 }

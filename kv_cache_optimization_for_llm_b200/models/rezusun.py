@@ -51,7 +51,9 @@ def _mixer(cfg: RezusunConfig, i: int, layer: RezusunLayerConfig) -> PartSpec:
         return PartSpec("latent_attention", {
             "hidden_size": W, "heads": int(m["heads"]), "dim": int(m["dim"]), "rot_dim": int(m["rot_dim"]),
             "vdim": int(m["vdim"]), "q_rank": int(m["q_rank"]), "kv_rank": int(m["kv_rank"]),
-            "scale": float(m["scale"]), "eps": cfg.norm_eps, "position": rope,
+            # the scores' factor; a file that leaves it out gets one over the root of a head's key size
+            "scale": float(m["scale"]) if m.get("scale") is not None else (int(m["dim"]) + int(m["rot_dim"])) ** -0.5,
+            "eps": cfg.norm_eps, "position": rope,
         }, {"dq": p + "dq", "dq_norm": p + "dq.norm", "uq": p + "uq", "dkv": p + "dkv", "dkv_norm": p + "dkv.norm",
             "uk": p + "uk", "uv": p + "uv", "sink": p + "sink", "o": p + "o"})
     if layer.type == "general_delta":

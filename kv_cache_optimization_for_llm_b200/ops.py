@@ -452,13 +452,28 @@ def latent_prep(d_in: torch.Tensor, q_rank: int, kv_off: int, rank: int, rot: in
     return cq
 
 
+HEAD_GEMM_LIBRARY_MIN_ROWS = int(os.environ.get('KVB200_HEAD_GEMM_LIBRARY_MIN_ROWS', '128'))
+
+
 def head_gemm(x: torch.Tensor, first: int, head_stride: int, w: torch.Tensor) -> torch.Tensor:
     """A product per head: ``out[t, h, :] = w[h] @ x[t, first + h * head_stride : ... + K]`` with
-    ``w`` [H, N, K]; float32 sums in ascending k.  Returns [T, H * N]."""
+    ``w`` [H, N, K].  float32, and bfloat16 steps of fewer than 128 rows: this package's FMA kernel, float32
+    sums in ascending k; bfloat16 with more rows: the library's batched product.  Returns [T, H * N]."""
     _need_cuda(x, w)
     H, N, K = w.shape
     assert w.is_contiguous() and w.dtype == x.dtype and x.stride(1) == 1
     out = new((x.shape[0], H * N), x.dtype, x.device)
+    T = x.shape[0]
+    if x.dtype == torch.bfloat16 and T >= HEAD_GEMM_LIBRARY_MIN_ROWS:
+        # many rows: the library's batched product (tensor cores, float32 sums), as the other products of such steps
+        xv = torch.as_strided(x, (H, T, K), (head_stride, x.stride(0), 1), x.storage_offset() + first)
+        tmp = new((H, T, N), x.dtype, x.device)
+        torch.bmm(xv, w.transpose(1, 2), out=tmp)
+        out.view(T, H, N).copy_(tmp.permute(1, 0, 2))
+        if _marks is not None:
+            _mark("head_gemm_library")
+        choices["head_gemm_library"] += 1
+        return out
     rc = lib("latent_attention").kvb_head_gemm(c_void_p(_at(x, first)), c_int(x.stride(0)), c_int(head_stride), _p(w),
                                                _p(out), c_int(out.stride(0)), c_int(N), c_int(x.shape[0]), c_int(N),
                                                c_int(K), c_int(H), c_int(dtype_code(x.dtype)), _stream())

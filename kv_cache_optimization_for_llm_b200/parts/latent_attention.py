@@ -69,7 +69,7 @@ class LatentAttention(Part):
 
     def activation_widths(self):
         H = self.heads
-        return [self.w_in.shape[0], self.q_rank, H * (self.dim + self.rot), 2 * H * self.rank, H * self.vdim,
+        return [self.w_in.shape[0], self.q_rank, H * (self.dim + self.rot), 3 * H * self.rank, 2 * H * self.vdim,
                 self.o.shape[0]]
 
     def query_tile_heights(self):

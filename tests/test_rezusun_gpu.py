@@ -522,3 +522,31 @@ def test_replay_through_the_trace_runner(dtype, flags):
                 step += 1
     finally:
         tr.close()
+
+
+def test_command_line_serves_the_design():
+    """The engine's command line on a Rezusun folder: requests on standard input in the wire format,
+    greedy tokens back as JSON lines; each token is the plain model's best (ties within 1e-4 allowed)."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    folder = tempfile.mkdtemp(prefix="kvb200_rz_")
+    cfg = tiny.MIXED
+    w = tiny.write_model(folder, cfg, seed=8)
+    rng = np.random.default_rng(4)
+    prompts = {3: rng.integers(0, cfg["vocab"], 9).tolist(), 11: rng.integers(0, cfg["vocab"], 26).tolist()}
+    lines = [f"{rid} 6 1 " + " ".join(map(str, toks)) for rid, toks in prompts.items()]
+    env = dict(os.environ, IGNORE_EOS="1", PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    p = subprocess.run([sys.executable, "-m", "kv_cache_optimization_for_llm_b200.cli", folder, "--dtype", "float32",
+                        "--page-size", "4", "--num-pages", "64", "--max-num-seqs", "4", "--max-model-len", "64"],
+                       input="\n".join(lines) + "\n", capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    out = [json.loads(line) for line in p.stdout.splitlines() if line.strip()]
+    for rid, prompt in prompts.items():
+        toks = [m["tok"] for m in out if m.get("id") == rid and "tok" in m]
+        assert len(toks) == 6
+        logits = R.forward(cfg, w, prompt + toks)
+        for j, tok in enumerate(toks):
+            row = logits[len(prompt) + j - 1]
+            assert row[tok] >= row.max() - 1e-4 * np.abs(row).max(), (rid, j)
