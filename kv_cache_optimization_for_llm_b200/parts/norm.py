@@ -21,7 +21,7 @@ class RMSNorm(Part):
 
     @classmethod
     def kernel_modules(cls, params, dtype):
-        return ("elementwise", "rowwise")
+        return ("elementwise",)      # the general kernel (rowwise) is loaded at first use, if a branch ever hands it a post norm
 
     def __init__(self, params, weights, ctx):
         super().__init__(params, weights, ctx)
