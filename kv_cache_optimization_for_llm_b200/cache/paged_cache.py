@@ -19,7 +19,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from .. import build
-from .specs import PagedKVBinding, PagedKVSpec, SlotStateBinding, SlotStateSpec
+from .specs import PagedKVBinding, PagedKVSpec, SlotStateBinding, SlotStateSpec, paged_part, state_part
 
 
 def host_runtime():
@@ -38,11 +38,13 @@ class PagedCache:
         group_keys: List[Tuple] = []
         self.entry_group: List[Optional[Tuple[int, int]]] = []  # (group, index inside it)
         counts: List[int] = []
-        for i, spec in enumerate(entry_specs):
-            if cache_of[i] is not None or not isinstance(spec, PagedKVSpec):
+        for i, wish in enumerate(entry_specs):
+            spec = paged_part(wish)
+            if cache_of[i] is not None or spec is None:
                 self.entry_group.append(None)
                 continue
-            key = (spec.num_kv_heads, spec.head_dim, spec.window or 0, int(spec.planes))
+            key = (spec.num_kv_heads, spec.head_dim, spec.window or 0, int(spec.planes),
+                   int(spec.keep_first) if spec.window else 0)
             if key not in group_keys:
                 group_keys.append(key)
                 counts.append(0)
@@ -53,7 +55,7 @@ class PagedCache:
             if src is not None:
                 if type(entry_specs[i]) is not type(entry_specs[src]):
                     raise ValueError(f"schedule entry {i} cannot read the cache of entry {src}: different kinds")
-                if isinstance(entry_specs[i], PagedKVSpec) and entry_specs[i] != entry_specs[src]:
+                if paged_part(entry_specs[i]) is not None and entry_specs[i] != entry_specs[src]:
                     raise ValueError(f"schedule entry {i} cannot read the cache of entry {src}: "
                                      f"{entry_specs[i]} against {entry_specs[src]}")
         self.group_keys = group_keys
@@ -61,10 +63,10 @@ class PagedCache:
         if not group_keys:
             # A model without paged mixers still gets one (empty) group, so that the
             # manager, the tables and the scheduler work unchanged.
-            self.group_keys = [(0, 0, 0, 2)]
+            self.group_keys = [(0, 0, 0, 2, 0)]
             self.group_entries = [0]
         self.manager = host.CacheManager(
-            [host.GroupSpec(self.page_size, key[2]) for key in self.group_keys],
+            [host.GroupSpec(self.page_size, key[2], key[4]) for key in self.group_keys],
             [self.num_pages] * len(self.group_keys), self.num_slots)
         self.max_pages = [(int(max_model_len) + self.page_size - 1) // self.page_size] * len(self.group_keys)
         self.kv: List[Optional[torch.Tensor]] = []
@@ -73,11 +75,12 @@ class PagedCache:
         if allocate:
             # One page and one slot more than the manager hands out: padding rows of a
             # fixed-shape (graph) batch write there.
-            for (nkv, d, _w, planes), n in zip(self.group_keys, self.group_entries):
+            for (nkv, d, _w, planes, _kf), n in zip(self.group_keys, self.group_entries):
                 self.kv.append(torch.zeros((max(n, 0), planes, self.num_pages + 1, nkv, self.page_size, d),
                                            dtype=dtype, device=self.device) if n else None)
-            for i, spec in enumerate(entry_specs):
-                if isinstance(spec, SlotStateSpec) and cache_of[i] is None:
+            for i, wish in enumerate(entry_specs):
+                spec = state_part(wish)
+                if spec is not None and cache_of[i] is None:
                     self.states[i] = torch.zeros((self.num_slots + 1,) + tuple(spec.shape), dtype=spec.dtype,
                                                  device=self.device)
 
@@ -92,23 +95,23 @@ class PagedCache:
     def bytes_per_page(self) -> int:
         esz = torch.empty((), dtype=self.dtype).element_size()
         return sum(n * planes * nkv * self.page_size * d * esz
-                   for (nkv, d, _, planes), n in zip(self.group_keys, self.group_entries))
+                   for (nkv, d, _, planes, _kf), n in zip(self.group_keys, self.group_entries))
 
     @staticmethod
     def bytes_per_token(entry_specs, cache_of, dtype) -> int:
         esz = torch.empty((), dtype=dtype).element_size()
-        return sum(s.planes * s.num_kv_heads * s.head_dim * esz for i, s in enumerate(entry_specs)
-                   if isinstance(s, PagedKVSpec) and cache_of[i] is None)
+        return sum(s.planes * s.num_kv_heads * s.head_dim * esz for i, s in enumerate(map(paged_part, entry_specs))
+                   if s is not None and cache_of[i] is None)
 
     def binding(self, entry: int):
         src = self._cache_of[entry]
         owner = entry if src is None else src
         spec = self._entry_specs[owner]
-        if isinstance(spec, PagedKVSpec):
+        if paged_part(spec) is not None:
             g, idx = self.entry_group[owner]
             t = self.kv[g]
             return PagedKVBinding(k=t[idx, 0], v=t[idx, 1] if t.shape[1] > 1 else None, group=g, page_size=self.page_size,
-                                  write=(src is None))
+                                  write=(src is None), state=self.states.get(owner))
         if isinstance(spec, SlotStateSpec):
             return SlotStateBinding(state=self.states[owner], write=(src is None))
         return None

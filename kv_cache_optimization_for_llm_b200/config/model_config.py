@@ -265,6 +265,105 @@ class RezusunConfig:
         return list(range(a)) + list(range(a, b)) * times + list(range(b, n))
 
 
+@dataclass(frozen=True)
+class SolulixLayerConfig:
+    """One entry of ``layers``: the mixer's kind (``attention`` or ``delta``) and sizes, and the
+    feed-forward (None: the layer has only its mixer)."""
+    type: str
+    mixer: Mapping[str, Any]
+    mlp: Optional[Mapping[str, Any]]
+
+
+_SOLULIX_MIXER_KEYS = {
+    "attention": ("heads", "kv_heads", "dim", "vdim", "conv", "scale", "mask"),
+    "delta": ("heads", "kv_heads", "dim", "vdim", "conv"),
+}
+
+
+@dataclass(frozen=True)
+class SolulixConfig:
+    """The keys of a Solulix config.json: ``vocab``, ``width``, ``norm.eps``, ``layers`` (each with
+    ``type``, ``mixer`` and ``mlp``, the latter of ``kind`` ``dense`` or ``moe``) and ``loop``
+    (layers start .. stop - 1 run ``times`` times in a row)."""
+    architecture: str
+    vocab: int
+    width: int
+    norm_eps: float
+    layers: Tuple[SolulixLayerConfig, ...]
+    loop: Optional[Tuple[int, int, int]]
+    max_position_embeddings: int
+    eos_token_ids: Tuple[int, ...] = field(default_factory=tuple)
+
+    @classmethod
+    def from_dict(cls, d: Mapping[str, Any]) -> "SolulixConfig":
+        norm = d.get("norm") or {}
+        layers = []
+        for i, entry in enumerate(d.get("layers") or []):
+            kind = entry.get("type")
+            if kind not in _SOLULIX_MIXER_KEYS:
+                raise ConfigError(f"config.json: layer {i} has a mixer of type {kind!r}; known: "
+                                  + ", ".join(sorted(_SOLULIX_MIXER_KEYS)))
+            mixer = entry.get("mixer") or {}
+            for key in _SOLULIX_MIXER_KEYS[kind]:
+                if mixer.get(key) is None:
+                    raise ConfigError(f"config.json: layer {i} ({kind}): mixer key {key!r} is missing")
+            if kind == "attention":
+                for key in ("size", "keep_first"):
+                    if mixer["mask"].get(key) is None:
+                        raise ConfigError(f"config.json: layer {i}: mask.{key} is missing")
+            mlp = entry.get("mlp")
+            if mlp is not None:
+                if mlp.get("kind") == "dense":
+                    _need(mlp, "ff", int)
+                elif mlp.get("kind") == "moe":
+                    router = mlp.get("router") or {}
+                    for key in ("experts", "top", "identity", "scale"):
+                        if router.get(key) is None:
+                            raise ConfigError(f"config.json: layer {i}: mlp.router.{key} is missing")
+                    if (mlp.get("expert") or {}).get("ff") is None:
+                        raise ConfigError(f"config.json: layer {i}: mlp.expert.ff is missing")
+                    if mlp.get("shared") is not None and mlp["shared"].get("ff") is None:
+                        raise ConfigError(f"config.json: layer {i}: mlp.shared.ff is missing")
+                    n_all = int(router["experts"]) + int(router["identity"])
+                    if not 1 <= int(router["top"]) <= n_all:
+                        raise ConfigError(f"config.json: layer {i}: the router chooses {router['top']} of {n_all} experts")
+                else:
+                    raise ConfigError(f"config.json: layer {i}: a feed-forward of kind {mlp.get('kind')!r} is not known "
+                                      "(known: 'dense', 'moe')")
+            layers.append(SolulixLayerConfig(str(kind), dict(mixer), dict(mlp) if mlp is not None else None))
+        if not layers:
+            raise ConfigError("config.json: 'layers' is missing or empty")
+        loop = d.get("loop")
+        loop_t = None
+        if loop:
+            loop_t = (_need(loop, "start", int), _need(loop, "stop", int), _need(loop, "times", int))
+            a, b, n = loop_t
+            if not (0 <= a <= b <= len(layers)) or n < 1:
+                raise ConfigError(f"config.json: loop {dict(loop)} does not fit {len(layers)} layers")
+            if a == b:
+                loop_t = None       # an empty run of layers: nothing repeats
+        eos = d.get("eos_token_id")
+        eos_ids = () if eos is None else (tuple(int(e) for e in eos) if isinstance(eos, (list, tuple)) else (int(eos),))
+        cfg = cls(architecture=str(d.get("architecture") or (d.get("architectures") or ["Solulix"])[0]),
+                  vocab=_need(d, "vocab", int), width=_need(d, "width", int), norm_eps=_need(norm, "eps", float),
+                  layers=tuple(layers), loop=loop_t,
+                  max_position_embeddings=int(d.get("max_position_embeddings") or 131072), eos_token_ids=eos_ids)
+        if cfg.vocab < 1 or cfg.width < 1 or not cfg.norm_eps > 0:
+            raise ConfigError("config.json: vocab and width must be positive and norm.eps above zero")
+        return cfg
+
+    def passes(self):
+        """(layer index, number of the pass that this run of the layer opens or None) in the order the layers run."""
+        n = len(self.layers)
+        if self.loop is None:
+            return [(i, None) for i in range(n)]
+        a, b, times = self.loop
+        order = [(i, None) for i in range(a)]
+        for t in range(times):
+            order += [(i, t if i == a else None) for i in range(a, b)]
+        return order + [(i, None) for i in range(b, n)]
+
+
 def read_config_json(model_dir) -> dict:
     path = Path(model_dir) / "config.json"
     if not path.exists():

@@ -12,10 +12,11 @@ PYBIND11_MODULE(_kvb_host, m) {
   m.doc() = "Host runtime: paged cache bookkeeping and the continuous-batching scheduler";
 
   py::class_<GroupSpec>(m, "GroupSpec")
-      .def(py::init([](int page_size, int window) { return GroupSpec{page_size, window}; }),
-           py::arg("page_size"), py::arg("window") = 0)
+      .def(py::init([](int page_size, int window, int keep_first) { return GroupSpec{page_size, window, keep_first}; }),
+           py::arg("page_size"), py::arg("window") = 0, py::arg("keep_first") = 0)
       .def_readwrite("page_size", &GroupSpec::page_size)
-      .def_readwrite("window", &GroupSpec::window);
+      .def_readwrite("window", &GroupSpec::window)
+      .def_readwrite("keep_first", &GroupSpec::keep_first);
 
   py::class_<CacheManager>(m, "CacheManager")
       .def(py::init<std::vector<GroupSpec>, std::vector<int>, int>(), py::arg("groups"),

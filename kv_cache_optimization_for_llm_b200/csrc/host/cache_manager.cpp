@@ -13,7 +13,7 @@ CacheManager::CacheManager(std::vector<GroupSpec> groups, std::vector<int> pages
     throw std::invalid_argument("CacheManager: one page count per group is required");
   if (num_slots < 1) throw std::invalid_argument("CacheManager: num_slots must be >= 1");
   for (size_t g = 0; g < groups_.size(); ++g) {
-    if (groups_[g].page_size < 1 || groups_[g].window < 0 || pages_per_group[g] < 1)
+    if (groups_[g].page_size < 1 || groups_[g].window < 0 || groups_[g].keep_first < 0 || pages_per_group[g] < 1)
       throw std::invalid_argument("CacheManager: bad geometry for group " + std::to_string(g));
     // Free list starts 0..N-1 and is popped from the back, as upstream's is
     // (paged_attention/src/engine.cu:216-217,376-382): a page given back is the
@@ -116,7 +116,9 @@ void CacheManager::advance(int64_t id, int computed) {
     if (groups_[g].window <= 0) continue;
     const int keep_from = first_needed_token((int)g, computed) / groups_[g].page_size;
     const int upto = std::min<int>(keep_from, (int)r.tables[g].size());
-    for (int lp = 0; lp < upto; ++lp) {
+    // pages that hold any of the first keep_first tokens stay for as long as the request lives
+    const int kept = (groups_[g].keep_first + groups_[g].page_size - 1) / groups_[g].page_size;
+    for (int lp = kept; lp < upto; ++lp) {
       if (r.tables[g][lp] < 0) continue;
       give_back((int)g, r.tables[g][lp]);
       r.tables[g][lp] = -1;

@@ -20,6 +20,7 @@ namespace kvb {
 struct GroupSpec {
   int page_size = 16;  // tokens per page
   int window = 0;      // 0: every key is kept; W>0: only the newest W keys are read
+  int keep_first = 0;  // with a window: the first keep_first keys of a sequence are read for good as well
 };
 
 class CacheManager {

@@ -7,7 +7,7 @@
 //   * MODE_GENERAL: decay d = exp(-e^{-1/2} sigmoid(z_d + b_d)) per key channel, removal along
 //     the unit key u = k / sqrt(|k|^2 + 1e-6) at the rate a = sigmoid(z_a + b_a):  p = a * u,
 //     x = u, c = v, read-out by r.
-//   * MODE_GATED: decay g = exp(-exp(A_h) softplus(z_d + b_d)) per key channel, unit q and k
+//   * MODE_GATED: decay g = exp(-exp(A_h) softplus(z_d + b_d)) per key channel (or one per head), unit q and k
 //     (q also times Dk^-1/2), write strength beta = sigmoid(z_b) per head; decaying first and
 //     then correcting the state's prediction for k is the same update with d = g, p = beta k,
 //     x = k * g, c = beta v, read-out by q.
@@ -57,6 +57,8 @@ struct DeltaArgs {
   int H, G, Dk, Dv;
   float eps;
   float* o_raw;                     // [T, H * Dv] float32 scratch: the read-outs before their norm
+  int decay_per_head;               // MODE_GATED: z_d is [T, H] and b_d [H], one decay for all key channels of a head
+  int gate_silu;                    // the output gate is silu(gate) instead of sigmoid(gate)
 };
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
@@ -122,7 +124,8 @@ __global__ void delta_scan_kernel(const DeltaArgs a, int n_scan, int cols_per_bl
           if (i < Dk) {
             kv = to_f32(kp[(size_t)t * a.ld_k + hk * Dk + i]);
             rv = to_f32(rp[(size_t)t * a.ld_r + hk * Dk + i]);
-            zd = to_f32(dp[(size_t)t * a.ld_decay + h * Dk + i]) + a.decay_bias[h * Dk + i];
+            const int di = a.decay_per_head ? h : h * Dk + i;
+            zd = to_f32(dp[(size_t)t * a.ld_decay + di]) + a.decay_bias[di];
             if (MODE == MODE_GENERAL) za = to_f32(xp[(size_t)t * a.ld_aux + h * Dk + i]) + a.aux_bias[h * Dk + i];
           }
           kr_[k][u] = kv; rr_[k][u] = rv; zd_[k][u] = zd; za_[k][u] = za;
@@ -282,7 +285,8 @@ __global__ void delta_finish_kernel(const DeltaArgs a, int T_) {
   const float inv = 1.0f / sqrtf(ss / (float)Dv + a.eps);
   for (int j = lane; j < Dv; j += 32) {
     const float w = a.norm_w[(a.norm_per_head ? h * Dv : 0) + j];
-    outp[j] = from_f32<T>(o[j] * inv * w * sigmoidf_(to_f32(gp[j])));
+    const float g = to_f32(gp[j]);
+    outp[j] = from_f32<T>(o[j] * inv * w * (a.gate_silu ? g * sigmoidf_(g) : sigmoidf_(g)));
   }
 }
 
@@ -369,7 +373,7 @@ __global__ void conv_silu_kernel(const T* __restrict__ in, int ld, const float* 
                                  const float* __restrict__ tails, long long slot_stride, T* __restrict__ out, int C,
                                  const int* __restrict__ positions, const int* __restrict__ token_req,
                                  const int* __restrict__ q_start, const int* __restrict__ req_start,
-                                 const int* __restrict__ slots) {
+                                 const int* __restrict__ slots, int act) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -381,7 +385,7 @@ __global__ void conv_silu_kernel(const T* __restrict__ in, int ld, const float* 
   float acc = 0.f;
   for (int j = 0; j < taps; ++j)
     acc = fmaf(w[(size_t)c * taps + j], conv_input(in, ld, tail, C, c, pos - (taps - 1) + j, start, row0, taps), acc);
-  out[(size_t)t * C + c] = from_f32<T>(acc / (1.0f + expf(-acc)));
+  out[(size_t)t * C + c] = from_f32<T>(act == 0 ? acc / (1.0f + expf(-acc)) : acc);
 }
 
 // After the convolution: the request's tail becomes the last taps - 1 inputs up to the end of the
@@ -409,18 +413,19 @@ __global__ void conv_tail_kernel(const T* __restrict__ in, int ld, int taps, flo
 }
 
 // in: [T, >= C] with row stride ld; w [C, taps] float32; tails: the tail of slot 0, slot_stride
-// floats from slot to slot, each [taps - 1, C]; out [T, C] dense.  Refuses taps > 16.
+// floats from slot to slot, each [taps - 1, C]; out [T, C] dense.  act: 0 SiLU behind the sum, 1 the
+// bare sum.  Refuses taps > 16.
 KVB_EXPORT int kvb_conv_silu(const void* in, int ld, const float* w, int taps, float* tails, long long slot_stride,
                              void* out, int C, int T_, int R, const int* positions, const int* token_req,
                              const int* q_start, const int* req_start, const int* ctx_len, const int* slots,
-                             int dtype, cudaStream_t stream) {
+                             int act, int dtype, cudaStream_t stream) {
   if (T_ <= 0 || R <= 0) return 0;
-  if (taps < 1 || taps - 1 > kMaxTail || C < 1) return KVB_ERR_BAD_SIZE;
+  if (taps < 1 || taps - 1 > kMaxTail || C < 1 || act < 0 || act > 1) return KVB_ERR_BAD_SIZE;
   const int threads = 128;
   const int by = (C + threads - 1) / threads;
   KVB_DISPATCH_DTYPE(dtype, T, {
     kvb_launch(conv_silu_kernel<T>, dim3(T_, by), dim3(threads), 0, stream, (const T*)in, ld, w, taps,
-               (const float*)tails, slot_stride, (T*)out, C, positions, token_req, q_start, req_start, slots);
+               (const float*)tails, slot_stride, (T*)out, C, positions, token_req, q_start, req_start, slots, act);
     if (taps > 1)
       kvb_launch(conv_tail_kernel<T>, dim3(R, by), dim3(threads), 0, stream, (const T*)in, ld, taps, tails, slot_stride,
                  C, q_start, req_start, ctx_len, slots);

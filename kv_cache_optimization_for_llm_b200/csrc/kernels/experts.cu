@@ -1,0 +1,173 @@
+// A feed-forward made of many small experts of which every token uses a few.
+//
+//   * route_kernel: the router.  One warp per token: logits z = W_r h in float32 (W_r float32, h as
+//     stored), scores s = softmax(z) over all experts, the `top` experts with the largest s + correction
+//     (ties go to the lower index), their weights s / (sum of the chosen s + 1e-20) * scale.  It
+//     leaves a dense table gate[t, e] (0 for an expert that was not chosen) and, for the last
+//     `identity` experts, which have no matrices and hand their input on, the sum of their weights.
+//   * expert_act_kernel: the experts' first products lie side by side in one row, [E * F | shared];
+//     a[t, j] = relu(p[t, j])^2 * gate[t, j / F] for j < E * F, relu(p)^2 behind it (an expert that
+//     every token uses).  One product with the experts' stacked second matrices then adds up the chosen
+//     experts' outputs, weighted, in its float32 accumulator; what an unchosen expert adds is exactly 0.
+//   * row_axpy_kernel: y[t] += c[t] * x[t], the identity experts' share.
+// Every sum is taken in an order that depends on the sizes only, so a token's result does not
+// depend on its neighbours in the step.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+constexpr int kRouteWarps = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(kRouteWarps * 32)
+route_kernel(const T* __restrict__ h, int ld_h, const float* __restrict__ w_router, const float* __restrict__ correction,
+             float* __restrict__ gate, float* __restrict__ identity_weight, int T_, int K, int E, int n_identity, int top,
+             float scale) {
+  extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouteWarps + warp;
+  if (t >= T_) return;
+  const int n_all = E + n_identity;
+  float* x = smem + (size_t)warp * (K + 2 * n_all);     // the token's input, float32
+  float* s = x + K;                                     // scores
+  float* c = s + n_all;                                 // choice scores; -inf once chosen
+  for (int k = lane; k < K; k += 32) x[k] = to_f32(h[(size_t)t * ld_h + k]);
+  __syncwarp();
+  float zmax = -CUDART_INF_F;
+  for (int e = 0; e < n_all; ++e) {
+    const float* wr = w_router + (size_t)e * K;
+    float part = 0.f;
+    for (int k = lane; k < K; k += 32) part = fmaf(wr[k], x[k], part);
+    const float z = warp_sum(part);
+    if (lane == 0) s[e] = z;
+    zmax = fmaxf(zmax, z);
+  }
+  __syncwarp();
+  float sum = 0.f;
+  for (int e = lane; e < n_all; e += 32) {
+    const float v = expf(s[e] - zmax);
+    s[e] = v;
+    sum += v;
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < n_all; e += 32) {
+    s[e] = s[e] / sum;
+    c[e] = s[e] + correction[e];
+    gate[(size_t)t * n_all + e] = 0.f;
+  }
+  __syncwarp();
+  // the chosen experts, one after the other; their indices end up in lane 0 .. top - 1's `mine`
+  int mine = -1;
+  float chosen_sum = 0.f;
+  for (int r = 0; r < top; ++r) {
+    float best = -CUDART_INF_F;
+    int at = 0x7fffffff;
+    for (int e = lane; e < n_all; e += 32)
+      if (c[e] > best) { best = c[e]; at = e; }       // ascending e: the lowest index among equals
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at == 0x7fffffff) break;                      // fewer experts than `top`
+    if (lane == r % 32 && r < 32) mine = at;
+    chosen_sum += s[at];
+    __syncwarp();
+    if (lane == 0) c[at] = -CUDART_INF_F;
+    __syncwarp();
+  }
+  const float norm = scale / (chosen_sum + 1e-20f);
+  float idw = 0.f;
+  for (int r = 0; r < top && r < 32; ++r) {
+    const int e = __shfl_sync(0xffffffffu, mine, r);
+    if (e < 0) continue;
+    const float g = s[e] * norm;
+    if (lane == 0) gate[(size_t)t * n_all + e] = g;
+    if (e >= E) idw += g;
+  }
+  if (lane == 0 && identity_weight) identity_weight[t] = idw;
+}
+
+// Refuses: more than 32 chosen experts per token, more than 4096 experts, K above 16384.
+KVB_EXPORT int kvb_route(const void* h, int ld_h, const float* w_router, const float* correction, float* gate,
+                         float* identity_weight, int T_, int K, int E, int n_identity, int top, float scale, int dtype,
+                         cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (E < 0 || n_identity < 0 || E + n_identity < 1 || E + n_identity > 4096 || top < 1 || top > 32 || K < 1 || K > 16384)
+    return KVB_ERR_BAD_SIZE;
+  const size_t smem = (size_t)kRouteWarps * (K + 2 * (E + n_identity)) * sizeof(float);
+  if (smem > 200 * 1024) return KVB_ERR_BAD_SIZE;
+  KVB_DISPATCH_DTYPE(dtype, T, {
+    if (smem > 48 * 1024) {
+      cudaError_t err = cudaFuncSetAttribute(route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return (int)err;
+    }
+    kvb_launch(route_kernel<T>, dim3((T_ + kRouteWarps - 1) / kRouteWarps), dim3(kRouteWarps * 32), smem, stream,
+               (const T*)h, ld_h, w_router, correction, gate, identity_weight, T_, K, E, n_identity, top, scale);
+  });
+  return kvb_launch_result();
+}
+
+// p [T, E * F + S]: the first products of the E routed experts (F features each) and of one expert that
+// every token uses (S features, may be 0).  gate [T, ld_gate] float32.  out [T, E * F + S] dense.
+template <typename T>
+__global__ void expert_act_kernel(const T* __restrict__ p, const float* __restrict__ gate, int ld_gate,
+                                  T* __restrict__ out, int EF, int F, int width, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / width;
+    const int j = (int)(idx - t * width);
+    const float g = j < EF ? gate[t * ld_gate + j / F] : 1.f;
+    float a = 0.f;
+    if (g != 0.f) {
+      const float z = fmaxf(to_f32(p[idx]), 0.f);
+      a = z * z * g;
+    }
+    out[idx] = from_f32<T>(a);
+  }
+}
+
+KVB_EXPORT int kvb_expert_act(const void* p, const float* gate, int ld_gate, void* out, int T_, int E, int F, int S,
+                              int dtype, cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  const int width = E * F + S;
+  if (E < 0 || F < 1 || S < 0 || width < 1) return KVB_ERR_BAD_SIZE;
+  const size_t total = (size_t)T_ * width;
+  const size_t want = (total + 255) / 256;
+  const int blocks = (int)(want < (size_t)kvb_sm_count() * 16 ? want : (size_t)kvb_sm_count() * 16);
+  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(expert_act_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)p, gate,
+                                            ld_gate, (T*)out, E * F, F, width, total)));
+  return kvb_launch_result();
+}
+
+// y[t, :] += c[t] * x[t, :]   (y [T, H] dense, x [T, >= H] with row stride ld_x)
+template <typename T>
+__global__ void row_axpy_kernel(T* __restrict__ y, const T* __restrict__ x, int ld_x, const float* __restrict__ c, int H,
+                                size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / H;
+    const int i = (int)(idx - t * H);
+    const float w = c[t];
+    if (w != 0.f) y[idx] = from_f32<T>(fmaf(w, to_f32(x[t * ld_x + i]), to_f32(y[idx])));
+  }
+}
+
+KVB_EXPORT int kvb_row_axpy(void* y, const void* x, int ld_x, const float* c, int T_, int H, int dtype,
+                            cudaStream_t stream) {
+  if (T_ <= 0 || H <= 0) return 0;
+  const size_t total = (size_t)T_ * H;
+  const size_t want = (total + 255) / 256;
+  const int blocks = (int)(want < (size_t)kvb_sm_count() * 16 ? want : (size_t)kvb_sm_count() * 16);
+  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(row_axpy_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)y, (const T*)x,
+                                            ld_x, c, H, total)));
+  return kvb_launch_result();
+}

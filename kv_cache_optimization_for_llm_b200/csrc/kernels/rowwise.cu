@@ -204,3 +204,64 @@ KVB_EXPORT int kvb_tanh_slice(const void* in, int ld, void* out, int T_, int n, 
                                             (T*)out, n, total)));
   return kvb_launch_result();
 }
+
+// ---------------------------------------------------------------- several summands join the residual, then a norm
+// For output row b (token row t = rows ? rows[b] : b):
+//   v = resid[t] + d1[t] + d2[t] + e[t] + vec        every summand optional: two branch outputs (a layer whose
+//                                                     sublayers read the same normed input), float32 rows (the
+//                                                     embedding's output re-entering), one float32 vector for all rows
+//   resid[t] = v                                      (only when every row is produced: rows == null)
+//   out[b] = v / sqrt(mean(v^2) + eps) * w            NORM_RMS; NORM_NONE: no output.  out is float32 when out_f32.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+join_norm_kernel(float* __restrict__ resid, const T* __restrict__ d1, const T* __restrict__ d2,
+                 const float* __restrict__ e, const float* __restrict__ vec, const float* __restrict__ w, int kind,
+                 float eps, void* __restrict__ out, int out_f32, const int* __restrict__ rows, int H) {
+  extern __shared__ float row[];
+  __shared__ float part[32];
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.x;
+  const size_t src = (size_t)(rows ? rows[b] : b) * H;
+  const bool any = d1 != nullptr || d2 != nullptr || e != nullptr || vec != nullptr;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float branches = 0.f;                          // the branches are summed first, then joined to the stream
+    if (d1) branches = to_f32(d1[src + i]);
+    if (d2) branches += to_f32(d2[src + i]);
+    float v = resid[src + i] + branches;
+    if (e) v += e[src + i];
+    if (vec) v += vec[i];
+    row[i] = v;
+    if (any && !rows) resid[src + i] = v;
+  }
+  if (kind == NORM_NONE) return;
+  __syncthreads();
+  float mean, rstd;
+  row_stats(row, H, kind, eps, part, mean, rstd);
+  if (out_f32) {
+    float* o = static_cast<float*>(out) + (size_t)b * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = (row[i] - mean) * rstd * (w ? w[i] : 1.f);
+  } else {
+    T* o = static_cast<T*>(out) + (size_t)b * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<T>((row[i] - mean) * rstd * (w ? w[i] : 1.f));
+  }
+}
+
+// dtype: the type of d1 and d2 (and of out unless out_f32).  Refuses rows wider than 51200.
+KVB_EXPORT int kvb_join_norm(float* resid, const void* d1, const void* d2, const float* e, const float* vec,
+                             const float* w, int kind, float eps, void* out, int out_f32, const int* rows,
+                             int n_out_rows, int H, int dtype, cudaStream_t stream) {
+  if (n_out_rows <= 0) return 0;
+  if (kind < 0 || kind > 2) return KVB_ERR_BAD_SIZE;
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 200 * 1024) return KVB_ERR_BAD_SIZE;
+  KVB_DISPATCH_DTYPE(dtype, T, {
+    if (smem > 48 * 1024) {
+      cudaError_t err = cudaFuncSetAttribute(join_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return (int)err;
+    }
+    kvb_launch(join_norm_kernel<T>, dim3(n_out_rows), dim3(kRowThreads), smem, stream, resid, (const T*)d1,
+               (const T*)d2, e, vec, w, kind, eps, out, out_f32, rows, H);
+  });
+  return kvb_launch_result();
+}

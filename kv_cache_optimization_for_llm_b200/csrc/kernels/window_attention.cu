@@ -1,0 +1,218 @@
+// Attention over a paged cache whose rows hold a token's key and value side by side, for
+// mixers that differ from the rotary kind in their mask and their softmax:
+//   * key and value sizes of their own (Dk, Dv); a cached row is [k (Dk) | v (Dv)] per token and
+//     key/value head, the pool being [pages, kv heads, page size, Dk + Dv];
+//   * a sliding window that also keeps the sequence's first tokens: query i sees key j when
+//     j <= i and (i - j < window or j < keep_first); window 0: every key up to i;
+//   * a softmax whose denominator may count one more (a key of score 0 that has no value):
+//     p_j = exp(s_j) / (1 + sum exp(s_j)).
+// Positions do not enter the scores here; a mixer that rotates does so before it calls.
+//
+// window_attention_kernel: one block per (query token, query head), any mix of runs and single
+// tokens; its four warps take the keys in chunks of 32 consecutive positions, chunk c going to
+// warp c % 4, so the sums a query sees follow absolute positions and do not depend on how its
+// request was cut into steps, on the batch or on where the pages lie.  Everything is float32
+// but the cached rows and the query as they are stored.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+constexpr int kMaxDim = 256;
+constexpr int kWarps = 4;
+
+// Writes the step's keys and values into their requests' pages.  src [T, >= ...] holds, per token, the
+// keys of all kv heads from column k_off on (G * Dk) and the values from v_off on (G * Dv).
+template <typename T>
+__global__ void kv_rows_append_kernel(const T* __restrict__ src, int ld, int k_off, int v_off, T* __restrict__ pages,
+                                      const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
+                                      const int* __restrict__ positions, const int* __restrict__ token_req, int G,
+                                      int Dk, int Dv, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, g = blockIdx.y;
+  const int pos = positions[t];
+  const int lp = pos / page_size;
+  const int page = lp < max_pages ? block_table[(size_t)token_req[t] * max_pages + lp] : -1;
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+    return;
+  }
+  T* row = pages + (((size_t)page * G + g) * page_size + (pos % page_size)) * (Dk + Dv);
+  const T* k = src + (size_t)t * ld + k_off + g * Dk;
+  const T* v = src + (size_t)t * ld + v_off + g * Dv;
+  for (int i = threadIdx.x; i < Dk; i += blockDim.x) row[i] = k[i];
+  for (int i = threadIdx.x; i < Dv; i += blockDim.x) row[Dk + i] = v[i];
+}
+
+KVB_EXPORT int kvb_kv_rows_append(const void* src, int ld, int k_off, int v_off, void* pages, const int* block_table,
+                                  int max_pages, int page_size, int num_pages, const int* positions,
+                                  const int* token_req, int T_, int G, int Dk, int Dv, int dtype, int* status,
+                                  cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (G < 1 || Dk < 1 || Dv < 1) return KVB_ERR_BAD_SIZE;
+  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(kv_rows_append_kernel<T>, dim3(T_, G), dim3(64), 0, stream, (const T*)src, ld,
+                                            k_off, v_off, (T*)pages, block_table, max_pages, page_size, num_pages,
+                                            positions, token_req, G, Dk, Dv, status)));
+  return kvb_launch_result();
+}
+
+// The dot product of the query (float32, shared memory) with a cached key; 16-byte loads when
+// the rows allow it.
+template <typename T>
+__device__ __forceinline__ float key_dot(const float* q_s, const T* k, int Dk, bool vec);
+
+template <>
+__device__ __forceinline__ float key_dot<float>(const float* q_s, const float* k, int Dk, bool vec) {
+  float dot = 0.f;
+  if (vec) {
+    for (int i = 0; i < Dk; i += 4) {
+      const float4 x = *reinterpret_cast<const float4*>(k + i);
+      dot = fmaf(q_s[i], x.x, dot); dot = fmaf(q_s[i + 1], x.y, dot);
+      dot = fmaf(q_s[i + 2], x.z, dot); dot = fmaf(q_s[i + 3], x.w, dot);
+    }
+  } else {
+    for (int i = 0; i < Dk; ++i) dot = fmaf(q_s[i], k[i], dot);
+  }
+  return dot;
+}
+
+template <>
+__device__ __forceinline__ float key_dot<__nv_bfloat16>(const float* q_s, const __nv_bfloat16* k, int Dk, bool vec) {
+  float dot = 0.f;
+  if (vec) {
+    for (int i = 0; i < Dk; i += 8) {
+      const uint4 x = *reinterpret_cast<const uint4*>(k + i);
+      const unsigned w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        dot = fmaf(q_s[i + 2 * u], __uint_as_float(w[u] << 16), dot);
+        dot = fmaf(q_s[i + 2 * u + 1], __uint_as_float(w[u] & 0xffff0000u), dot);
+      }
+    }
+  } else {
+    for (int i = 0; i < Dk; ++i) dot = fmaf(q_s[i], __bfloat162float(k[i]), dot);
+  }
+  return dot;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+window_attention_kernel(const T* __restrict__ q_base, int q_row_stride, const T* __restrict__ pages,
+                        const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
+                        const int* __restrict__ positions, const int* __restrict__ token_req, T* __restrict__ out,
+                        int nq, int nkv, int Dk, int Dv, float scale, int window, int keep_first, int one_more,
+                        int vec, int* status) {
+  __shared__ float q_s[kMaxDim];
+  __shared__ float acc_s[kWarps][kMaxDim];
+  __shared__ float m_s[kWarps], l_s[kWarps];
+
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int hk = h / (nq / nkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos = positions[t];
+  const int* table = block_table + (size_t)token_req[t] * max_pages;
+  const int row_len = Dk + Dv;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;      // first key of the window
+  const int keep = window > 0 ? keep_first : 0;                  // keys below it are seen whatever the window
+  const int keep_chunks = (keep + 31) / 32;
+  const int lo_chunk = lo / 32;
+
+  const T* q = q_base + (size_t)t * q_row_stride + (size_t)h * Dk;
+  for (int i = threadIdx.x; i < Dk; i += blockDim.x) q_s[i] = to_f32(q[i]);
+  __syncthreads();
+
+  float m = -CUDART_INF_F, l = 0.f;
+  float acc[kMaxDim / 32];
+#pragma unroll
+  for (int r = 0; r < kMaxDim / 32; ++r) acc[r] = 0.f;
+
+  for (int c = warp; c * 32 <= pos; c += kWarps) {
+    if (c >= keep_chunks && c < lo_chunk) {
+      // between the kept first tokens and the window: on to this warp's first chunk of the window
+      c += (lo_chunk - c + kWarps - 1) / kWarps * kWarps - kWarps;
+      continue;
+    }
+    const int j = c * 32 + lane;
+    const bool valid = j <= pos && (j >= lo || j < keep);
+    long long off = -1;
+    float s = -CUDART_INF_F;
+    if (valid) {
+      const int lp = j / page_size;
+      const int page = lp < max_pages ? table[lp] : -1;
+      if (page < 0 || page >= num_pages) {
+        atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+      } else {
+        off = (((long long)page * nkv + hk) * page_size + (j % page_size)) * row_len;
+        s = key_dot<T>(q_s, pages + off, Dk, vec != 0) * scale;
+      }
+    }
+    const float cm = warp_max(s);
+    if (cm == -CUDART_INF_F) continue;
+    const float m_new = fmaxf(m, cm);
+    const float corr = (m == -CUDART_INF_F) ? 0.f : expf(m - m_new);
+    const float p = (off >= 0) ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int r = 0; r < kMaxDim / 32; ++r) acc[r] *= corr;
+    const int n_in_chunk = min(32, pos - c * 32 + 1);
+    for (int jj = 0; jj < n_in_chunk; ++jj) {
+      const long long oj = __shfl_sync(0xffffffffu, off, jj);
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      if (oj < 0) continue;
+      const T* v = pages + oj + Dk;
+#pragma unroll
+      for (int r = 0; r < kMaxDim / 32; ++r) {
+        const int i = r * 32 + lane;
+        if (i < Dv) acc[r] = fmaf(pj, to_f32(v[i]), acc[r]);
+      }
+    }
+    m = m_new;
+  }
+
+  if (lane == 0) { m_s[warp] = m; l_s[warp] = l; }
+#pragma unroll
+  for (int r = 0; r < kMaxDim / 32; ++r) {
+    const int i = r * 32 + lane;
+    if (i < Dv) acc_s[warp][i] = acc[r];
+  }
+  __syncthreads();
+  if (warp == 0) {
+    float M = one_more ? 0.f : -CUDART_INF_F;       // the one more key's score is 0
+    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, m_s[w]);
+    float L = one_more ? expf(-M) : 0.f, f[kWarps];
+    for (int w = 0; w < kWarps; ++w) {
+      f[w] = (m_s[w] == -CUDART_INF_F) ? 0.f : expf(m_s[w] - M);
+      L += l_s[w] * f[w];
+    }
+    T* o = out + ((size_t)t * nq + h) * Dv;
+    for (int i = lane; i < Dv; i += 32) {
+      float a = 0.f;
+      for (int w = 0; w < kWarps; ++w) a += acc_s[w][i] * f[w];
+      o[i] = from_f32<T>(L > 0.f ? a / L : 0.f);
+    }
+  }
+}
+
+// q points at the first query head of token 0; consecutive tokens are q_row_stride elements apart.
+// pages: [num_pages, nkv, page_size, Dk + Dv].  out is [T, nq * Dv], dense.
+// Refuses: Dk or Dv above 256, nq not a multiple of nkv, a negative window or keep_first.
+KVB_EXPORT int kvb_window_attention(const void* q, int q_row_stride, const void* pages, const int* block_table,
+                                    int max_pages, int page_size, int num_pages, const int* positions,
+                                    const int* token_req, void* out, int T_, int nq, int nkv, int Dk, int Dv,
+                                    float scale, int window, int keep_first, int one_more, int dtype, int* status,
+                                    cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (Dk > kMaxDim || Dv > kMaxDim || Dk < 1 || Dv < 1 || nkv < 1 || nq % nkv || window < 0 || keep_first < 0)
+    return KVB_ERR_BAD_SIZE;
+  const int esz = dtype == KVB_F32 ? 4 : 2;
+  const int per16 = 16 / esz;
+  const int vec = (Dk % per16 == 0 && (Dk + Dv) % per16 == 0 && ((uintptr_t)pages % 16) == 0) ? 1 : 0;
+  dim3 grid(T_, nq);
+  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(window_attention_kernel<T>, grid, dim3(kWarps * 32), 0, stream, (const T*)q,
+                                            q_row_stride, (const T*)pages, block_table, max_pages, page_size, num_pages,
+                                            positions, token_req, (T*)out, nq, nkv, Dk, Dv, scale, window, keep_first,
+                                            one_more, vec, status)));
+  return kvb_launch_result();
+}

@@ -41,6 +41,9 @@ class DecoderModel:
         self.final_norm = make("norm", spec.final_norm)
         self.head = make("head", spec.lm_head)
         self.schedule = list(spec.schedule)
+        # parts that stand in the schedule in front of a layer (the start of a pass through repeated layers)
+        self.before = [make("stream", e.before) if e.before is not None else None for e in self.schedule]
+        self.keeps_embedding = any(getattr(b, "needs_embedding", False) for b in self.before)
 
     def cache_specs(self):
         """Per schedule entry: what its mixer asks of the cache, and whose cache it reads."""
@@ -62,13 +65,21 @@ class DecoderModel:
             return self._forward(batch, cache, arena)
 
     def _forward(self, batch, cache, arena) -> torch.Tensor:
+        from .. import ops
         if arena is not None:
             arena.begin_step()
         residual = self.embedding.forward(batch)
+        embedded = None
+        if self.keeps_embedding:
+            # the residual is updated in place from the first layer on: what enters the stream again later is a copy
+            embedded = ops.new(tuple(residual.shape), residual.dtype, residual.device)
+            embedded.copy_(residual)
         delta = None
         for i, entry in enumerate(self.schedule):
             if arena is not None:
                 arena.begin_layer()
+            if self.before[i] is not None:
+                delta = self.before[i].forward(residual, delta, embedded)
             residual, delta = self.layers[entry.layer].forward(residual, delta, batch, cache.binding(i))
         if arena is not None:
             arena.end_layers()
@@ -84,7 +95,7 @@ class DecoderModel:
         (``activation_widths``; a part that declares none is taken as eight rows of the model's
         width) in the compute precision, plus a fifth."""
         h, v = self.spec.hidden_size, self.spec.vocab_size
-        step = 4 * max_tokens * h + max_logit_rows * 4 * (h + v) + (1 << 16)
+        step = 4 * max_tokens * h * (2 if self.keeps_embedding else 1) + max_logit_rows * 4 * (h + v) + (1 << 16)
         per_layer = 0
         for block in self.layers:
             widths = 0

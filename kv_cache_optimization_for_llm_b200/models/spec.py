@@ -42,9 +42,12 @@ class LayerSpec:
 @dataclass
 class ScheduleEntry:
     """One application of a layer.  ``cache_of``: index of an earlier schedule entry
-    whose cache this application reads instead of keeping one of its own."""
+    whose cache this application reads instead of keeping one of its own.  ``before``: a part
+    of the ``stream`` family that touches the residual stream right before this application
+    (what a repeated run of layers adds at the start of each pass)."""
     layer: int
     cache_of: Optional[int] = None
+    before: Optional[PartSpec] = None
 
 
 @dataclass
@@ -115,6 +118,9 @@ def iter_parts(spec: ModelSpec):
                              f"missing {missing}, not taken {extra}")
         for name, family in families.items():
             yield from _with_nested(family, layer.parts[name])
+    for entry in spec.schedule:
+        if entry.before is not None:
+            yield from _with_nested("stream", entry.before)
     yield from _with_nested("norm", spec.final_norm)
     yield from _with_nested("head", spec.lm_head)
 

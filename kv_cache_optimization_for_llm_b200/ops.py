@@ -346,6 +346,53 @@ def tanh_slice(x: torch.Tensor, first: int, n: int) -> torch.Tensor:
     return out
 
 
+class PendingSum:
+    """What still has to join the float32 residual stream before the next norm reads it: up to two
+    branch outputs ``deltas`` [T, H] of the compute type (a layer whose mixer and feed-forward read
+    the same normed input hands on both), float32 ``rows`` [T, H] (the embedding's output entering
+    the stream again at the start of a repeated run of layers) and a float32 ``vector`` [H] added to
+    every row.  :func:`join_norm` adds them all and norms the sum in one kernel."""
+    __slots__ = ("deltas", "rows", "vector")
+
+    def __init__(self, deltas=(), rows=None, vector=None):
+        self.deltas = tuple(d for d in deltas if d is not None)
+        assert len(self.deltas) <= 2
+        self.rows, self.vector = rows, vector
+
+    def plus(self, rows=None, vector=None) -> "PendingSum":
+        assert (rows is None or self.rows is None) and (vector is None or self.vector is None)
+        return PendingSum(self.deltas, self.rows if rows is None else rows, self.vector if vector is None else vector)
+
+
+def join_norm(resid: torch.Tensor, pending: Optional[PendingSum], kind: Optional[str], weight: Optional[torch.Tensor],
+              eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
+              compute_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """``resid += sum of pending`` in float32 (in place unless ``rows`` selects), then the norm ``kind``
+    ("rms", "layer" or None for no output) of the sum times ``weight``.  ``out_dtype`` may be float32
+    whatever the type of the pending branch outputs (``compute_dtype`` names that type when there
+    are none)."""
+    _need_cuda(resid)
+    assert resid.dtype == torch.float32 and resid.is_contiguous()
+    T, H = resid.shape
+    deltas = pending.deltas if pending is not None else ()
+    e = pending.rows if pending is not None else None
+    vec = pending.vector if pending is not None else None
+    dt = deltas[0].dtype if deltas else (compute_dtype or out_dtype)
+    for d in deltas:
+        assert d.shape == resid.shape and d.is_contiguous() and d.dtype == dt
+    assert e is None or (e.dtype == torch.float32 and e.shape == resid.shape and e.is_contiguous())
+    assert vec is None or (vec.dtype == torch.float32 and vec.numel() == H and vec.is_contiguous())
+    assert out_dtype in (dt, torch.float32)
+    n = T if rows is None else rows.numel()
+    out = new((n, H), out_dtype, resid.device) if kind is not None else None
+    rc = lib("rowwise").kvb_join_norm(_p(resid), _p(deltas[0] if deltas else None), _p(deltas[1] if len(deltas) > 1 else None),
+                                      _p(e), _p(vec), _p(weight), c_int(NORM_KINDS[kind]), c_float(eps), _p(out),
+                                      c_int(1 if out_dtype == torch.float32 else 0), _p(rows), c_int(n), c_int(H),
+                                      c_int(dtype_code(dt)), _stream())
+    _check(rc, "join_norm")
+    return out
+
+
 # ------------------------------------------------------------------ mixers with a matrix state (delta-rule family)
 
 class _DeltaArgs(ctypes.Structure):
@@ -355,7 +402,7 @@ class _DeltaArgs(ctypes.Structure):
                 ("head_rate", c_void_p), ("norm_w", c_void_p), ("norm_per_head", c_int), ("state", c_void_p),
                 ("slot_stride", c_longlong), ("out", c_void_p), ("ld_out", c_int), ("q_start", c_void_p),
                 ("req_start", c_void_p), ("slots", c_void_p), ("H", c_int), ("G", c_int), ("Dk", c_int), ("Dv", c_int),
-                ("eps", c_float), ("o_raw", c_void_p)]
+                ("eps", c_float), ("o_raw", c_void_p), ("decay_per_head", c_int), ("gate_silu", c_int)]
 
 
 _key_pad: Dict[int, int] = {}
@@ -373,13 +420,16 @@ def _at(t: torch.Tensor, col: int) -> int:
 
 
 def delta_scan(mode: str, batch, state: torch.Tensor, r, k, v, gate, decay, aux, decay_bias, aux_bias, head_rate,
-               norm_w, norm_per_head: bool, heads: int, key_heads: int, dk: int, dv: int, eps: float) -> torch.Tensor:
+               norm_w, norm_per_head: bool, heads: int, key_heads: int, dk: int, dv: int, eps: float,
+               decay_per_head: bool = False, gate_act: str = "sigmoid") -> torch.Tensor:
     """One step of a delta-rule mixer for every request of the batch: walks each request's new
     tokens in order from the state in its slot (zero for a request that starts at position 0)
     and leaves the new state there.  ``r, k, v, gate, decay, aux``: (tensor, first column) pairs
     naming where each projection lies in a [T, *] tensor of the compute type.  ``state``:
     float32 [slots, >= heads * dv * delta_key_pad(dk)], a request's slot row starting with the
     matrix states.  ``mode``: "general" or "gated" (see csrc/kernels/delta_rule.cu).
+    ``decay_per_head`` ("gated"): ``decay`` is [T, heads] and ``decay_bias`` [heads], one decay for all key
+    channels of a head.  ``gate_act``: "sigmoid" or "silu", the function applied to the output gate.
     Returns the gated, normed read-out [T, heads * dv]."""
     x0 = r[0]
     _need_cuda(x0, state)
@@ -400,6 +450,8 @@ def delta_scan(mode: str, batch, state: torch.Tensor, r, k, v, gate, decay, aux,
     a.q_start, a.req_start, a.slots = batch.q_start.data_ptr(), batch.req_start.data_ptr(), batch.slots.data_ptr()
     a.H, a.G, a.Dk, a.Dv, a.eps = heads, key_heads, dk, dv, eps
     a.o_raw = new((T, heads * dv), torch.float32, x0.device).data_ptr()
+    a.decay_per_head = 1 if decay_per_head else 0
+    a.gate_silu = {"sigmoid": 0, "silu": 1}[gate_act]
     rc = lib("delta_rule").kvb_delta_scan(ctypes.byref(a), c_int({"general": 0, "gated": 1}[mode]),
                                           c_int(batch.num_reqs), c_int(T), c_int(int(getattr(batch, "max_q_len", 0) or 0)),
                                           c_int(dtype_code(x0.dtype)), _stream())
@@ -411,8 +463,8 @@ def delta_scan(mode: str, batch, state: torch.Tensor, r, k, v, gate, decay, aux,
 
 
 def conv_silu(x: torch.Tensor, first: int, channels: int, w: torch.Tensor, tails: Optional[torch.Tensor],
-              batch) -> torch.Tensor:
-    """``silu`` of a short causal convolution over time per channel of ``x[:, first:first + channels]``.
+              batch, act: str = "silu") -> torch.Tensor:
+    """``silu`` (``act`` "none": nothing) of a short causal convolution over time per channel of ``x[:, first:first + channels]``.
     ``w`` float32 [channels, taps], last column for the token itself.  ``tails``: float32
     [slots, >= (taps - 1) * channels], a view whose row r starts with request slot r's last
     ``taps - 1`` inputs; it is read for the inputs in front of the step's tokens and brought up to date."""
@@ -425,7 +477,7 @@ def conv_silu(x: torch.Tensor, first: int, channels: int, w: torch.Tensor, tails
         c_void_p(_at(x, first)), c_int(x.stride(0)), _p(w), c_int(taps), _p(tails),
         c_longlong(0 if tails is None else tails.stride(0)), _p(out), c_int(channels), c_int(x.shape[0]),
         c_int(batch.num_reqs), _p(batch.positions), _p(batch.token_req), _p(batch.q_start), _p(batch.req_start),
-        _p(batch.ctx_len), _p(batch.slots), c_int(dtype_code(x.dtype)), _stream())
+        _p(batch.ctx_len), _p(batch.slots), c_int({"silu": 0, "none": 1}[act]), c_int(dtype_code(x.dtype)), _stream())
     _check(rc, "conv_silu")
     global launch_count
     launch_count += 1 if taps > 1 else 0   # the convolution and the tails' update
@@ -580,6 +632,85 @@ def paged_attention_generic(qkv, k_pages, v_pages, block_table, positions, token
     _check(rc, "paged_attention_generic")
     choices["paged_attention_generic"] += 1
     return out
+
+
+def kv_rows_append(src: torch.Tensor, k_off: int, v_off: int, pages: torch.Tensor, block_table, batch,
+                   kv_heads: int, dk: int, dv: int) -> None:
+    """Writes the step's keys (``src[:, k_off : k_off + kv_heads * dk]``) and values (from ``v_off``) into the
+    requests' pages, whose rows hold a token's key and value side by side:
+    ``pages`` [num_pages, kv_heads, page_size, dk + dv]."""
+    _need_cuda(src, pages)
+    assert src.stride(1) == 1 and pages.is_contiguous() and pages.dtype == src.dtype
+    assert tuple(pages.shape[1:]) == (kv_heads, pages.shape[2], dk + dv)
+    rc = lib("window_attention").kvb_kv_rows_append(
+        _p(src), c_int(src.stride(0)), c_int(k_off), c_int(v_off), _p(pages), _p(block_table), c_int(block_table.shape[1]),
+        c_int(pages.shape[2]), c_int(pages.shape[0]), _p(batch.positions), _p(batch.token_req), c_int(src.shape[0]),
+        c_int(kv_heads), c_int(dk), c_int(dv), c_int(dtype_code(src.dtype)), _p(batch.status), _stream())
+    _check(rc, "kv_rows_append")
+
+
+def window_attention(q: torch.Tensor, q_off: int, pages: torch.Tensor, block_table, batch, heads: int, kv_heads: int,
+                     dk: int, dv: int, scale: float, window: int, keep_first: int, one_more: bool) -> torch.Tensor:
+    """Attention of every token (queries at ``q[:, q_off : q_off + heads * dk]``) over its request's cached
+    rows [key | value]: query i sees key j when ``j <= i and (i - j < window or j < keep_first)`` (``window``
+    0: every key up to i); ``one_more``: the softmax's denominator is ``1 + sum exp(s)``.  Positions do
+    not enter the scores.  Returns [T, heads * dv]."""
+    _need_cuda(q, pages)
+    assert q.stride(1) == 1 and pages.is_contiguous() and pages.dtype == q.dtype
+    T = q.shape[0]
+    out = new((T, heads * dv), q.dtype, q.device)
+    rc = lib("window_attention").kvb_window_attention(
+        c_void_p(_at(q, q_off)), c_int(q.stride(0)), _p(pages), _p(block_table), c_int(block_table.shape[1]),
+        c_int(pages.shape[2]), c_int(pages.shape[0]), _p(batch.positions), _p(batch.token_req), _p(out), c_int(T),
+        c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv), c_float(scale), c_int(int(window or 0)),
+        c_int(int(keep_first or 0)), c_int(1 if one_more else 0), c_int(dtype_code(q.dtype)), _p(batch.status), _stream())
+    _check(rc, "window_attention")
+    choices["window_attention"] += 1
+    return out
+
+
+# ------------------------------------------------------------------ routed experts
+
+def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, experts: int, identity: int, top: int,
+          scale: float):
+    """The router of a feed-forward of many experts.  ``w_router`` float32 [experts + identity, K],
+    ``correction`` float32 [experts + identity] (added to the scores for the choice only).  Returns
+    ``gate`` float32 [T, experts + identity], a token's weight for every expert (0 where not chosen), and
+    float32 [T], the summed weights of its identity experts (None without any)."""
+    _need_cuda(h, w_router)
+    T, K = h.shape
+    n_all = experts + identity
+    assert w_router.dtype == torch.float32 and w_router.is_contiguous() and tuple(w_router.shape) == (n_all, K)
+    assert correction.dtype == torch.float32 and correction.numel() == n_all and h.stride(1) == 1
+    gate = new((T, n_all), torch.float32, h.device)
+    idw = new((T,), torch.float32, h.device) if identity else None
+    rc = lib("experts").kvb_route(_p(h), c_int(h.stride(0)), _p(w_router), _p(correction), _p(gate), _p(idw), c_int(T),
+                                  c_int(K), c_int(experts), c_int(identity), c_int(top), c_float(scale),
+                                  c_int(dtype_code(h.dtype)), _stream())
+    _check(rc, "route")
+    return gate, idw
+
+
+def expert_act(p: torch.Tensor, gate: torch.Tensor, experts: int, ff: int, shared_ff: int) -> torch.Tensor:
+    """``relu(p)^2`` times each routed expert's weight for the token (``p`` [T, experts * ff + shared_ff]:
+    the experts' first products side by side, then those of an expert that every token uses)."""
+    _need_cuda(p, gate)
+    assert p.is_contiguous() and p.shape[1] == experts * ff + shared_ff and gate.dtype == torch.float32
+    out = new(tuple(p.shape), p.dtype, p.device)
+    rc = lib("experts").kvb_expert_act(_p(p), _p(gate), c_int(gate.stride(0)), _p(out), c_int(p.shape[0]), c_int(experts),
+                                       c_int(ff), c_int(shared_ff), c_int(dtype_code(p.dtype)), _stream())
+    _check(rc, "expert_act")
+    return out
+
+
+def row_axpy(y: torch.Tensor, x: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
+    """``y[t] += c[t] * x[t]`` in place (``c`` float32 [T])."""
+    _need_cuda(y, x, c)
+    assert y.is_contiguous() and x.stride(1) == 1 and x.dtype == y.dtype and x.shape == y.shape and c.dtype == torch.float32
+    rc = lib("experts").kvb_row_axpy(_p(y), _p(x), c_int(x.stride(0)), _p(c), c_int(y.shape[0]), c_int(y.shape[1]),
+                                     c_int(dtype_code(y.dtype)), _stream())
+    _check(rc, "row_axpy")
+    return y
 
 
 # ------------------------------------------------------------------ matrix products

@@ -18,6 +18,9 @@ nothing of the model it sits in.  Interfaces by family:
 * a mixer or feed-forward may set ``fuses_residual = True``; it then has
   ``fold_input_scale(vector)``, and its ``forward`` also takes ``into=residual`` and may get
   ``x`` as an ``ops.PendingNorm`` (see the prenorm block)
+* stream:        ``forward(residual, delta, embedded) -> delta``: stands in the schedule in front of a layer and
+                 changes what is pending on the residual stream (``embedded``: the embedding's output,
+                 kept for the step when a stream part sets ``needs_embedding``)
 * embedding:     ``forward(batch) -> residual``  (float32 [T, hidden])
 * head:          ``forward(x) -> logits``  (float32 [rows, vocab])
 """

@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import torch
 
+from .. import ops
 from .base import Part
 from .registry import register
 
@@ -92,3 +93,34 @@ class SandwichMixerBlock(SandwichBlock):
     """The sandwich block of a layer that has no feed-forward: ``h += post1(mixer(pre1(h)))``."""
 
     part_families = {"mixer": "mixer", "mixer_norm": "norm", "mixer_post_norm": "norm"}
+
+
+@register("block", "parallel")
+class ParallelBlock(Part):
+    """``h += mixer(norm(h)) + ff(norm(h))``: one norm, whose output both sublayers read.  The two
+    branch outputs travel on together as an :class:`ops.PendingSum`; the next norm (of the next
+    layer, or the model's last one) adds both to the float32 residual and norms the sum in one
+    kernel."""
+
+    part_families = {"mixer": "mixer", "norm": "norm", "feed_forward": "feed_forward"}
+
+    def __init__(self, parts):
+        self.parts = dict(parts)
+        self.mixer, self.norm = parts["mixer"], parts["norm"]
+        self.feed_forward = parts.get("feed_forward")
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, residual, delta, batch, cache):
+        x = self.norm.forward(residual, delta)
+        a = self.mixer.forward(x, batch, cache)
+        f = self.feed_forward.forward(x, batch) if self.feed_forward is not None else None
+        return residual, ops.PendingSum((a, f))
+
+
+@register("block", "parallel_mixer_only")
+class ParallelMixerBlock(ParallelBlock):
+    """The parallel block of a layer that has no feed-forward: ``h += mixer(norm(h))``."""
+
+    part_families = {"mixer": "mixer", "norm": "norm"}

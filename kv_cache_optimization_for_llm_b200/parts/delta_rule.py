@@ -166,3 +166,71 @@ class ChannelDelta(Part):
                            (p, self.at_b), self.dt_bias, None, self.A_log, self.norm, False,
                            self.heads, self.kv_heads, self.dim, self.vdim, self.eps)
         return ops.linear(y, self.o)
+
+
+@register("mixer", "gated_delta")
+class GatedDelta(Part):
+    """Gated delta rule with one decay per head.  q, k (``kv_heads`` heads of ``dim``) and v (``heads``
+    heads of ``vdim``) each pass a short causal convolution over time per channel (``conv`` taps, the
+    last for the token itself) and SiLU; q and k become unit vectors per head (q also times dim^-1/2);
+    head j reads q/k head ``j // (heads / kv_heads)``.  With ``beta = sigmoid(W_b h)`` and
+    ``g = exp(-exp(A_j) softplus(W_a h + dt_bias))``, both one number per head:
+
+        S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q.
+
+    Each head's o is divided by its root mean square, multiplied by ``norm`` (``vdim`` wide, the same
+    for all heads) and by ``silu(W_g h)``, then projected by W_o.  The request's state is the
+    matrices (float32) and the last ``conv - 1`` inputs of the convolutions.  One product makes every
+    projection; the recurrence runs in the scan kernel that the other delta-rule mixers use.
+    params: hidden_size, heads, kv_heads, dim, vdim, conv, eps."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        h, H, G, D, Dv, taps = (params[k] for k in ("hidden_size", "heads", "kv_heads", "dim", "vdim", "conv"))
+        return {"q": WeightSpec((G * D, h)), "k": WeightSpec((G * D, h)), "v": WeightSpec((H * Dv, h)),
+                "q_conv": WeightSpec((G * D, taps), "bias"), "k_conv": WeightSpec((G * D, taps), "bias"),
+                "v_conv": WeightSpec((H * Dv, taps), "bias"), "b": WeightSpec((H, h)), "a": WeightSpec((H, h)),
+                "A_log": WeightSpec((H,), "bias"), "dt_bias": WeightSpec((H,), "bias"),
+                "norm": WeightSpec((Dv,), "vector"), "g": WeightSpec((H * Dv, h)), "o": WeightSpec((h, H * Dv))}
+
+    @classmethod
+    def kernel_modules(cls, params, dtype):
+        return _modules(dtype)
+
+    def __init__(self, params, weights, ctx):
+        super().__init__(params, weights, ctx)
+        self.heads, self.kv_heads = int(params["heads"]), int(params["kv_heads"])
+        self.dim, self.vdim, self.taps = int(params["dim"]), int(params["vdim"]), int(params["conv"])
+        self.eps = float(params["eps"])
+        if self.heads % self.kv_heads:
+            raise ValueError(f"gated_delta: {self.heads} heads cannot share {self.kv_heads} query/key heads evenly")
+        self.pad = ops.delta_key_pad(self.dim)
+        if not self.pad or self.dim > 128 or self.vdim > 256 or (self.dim > 64 and self.vdim > 128):
+            raise ValueError(f"gated_delta: head sizes {self.dim} x {self.vdim} are refused by the scan kernel")
+        if not 1 <= self.taps <= 16:
+            raise ValueError(f"gated_delta: {self.taps} convolution taps are refused (1 to 16)")
+        gd, hv = self.kv_heads * self.dim, self.heads * self.vdim
+        qkv = torch.cat([weights["q"], weights["k"], weights["v"]], dim=0)
+        self.w_in, (_, self.at_b, self.at_a, self.at_g) = _stack([qkv, weights["b"], weights["a"], weights["g"]], ctx.dtype)
+        self.channels = 2 * gd + hv
+        self.conv_w = torch.cat([weights["q_conv"], weights["k_conv"], weights["v_conv"]], dim=0).contiguous()
+        self.A_log, self.dt_bias, self.norm, self.o = weights["A_log"], weights["dt_bias"], weights["norm"], weights["o"]
+        self.matrix_floats = self.heads * self.vdim * self.pad
+
+    def cache_spec(self):
+        return SlotStateSpec((self.matrix_floats + (self.taps - 1) * self.channels,), torch.float32)
+
+    def activation_widths(self):
+        hv = self.heads * self.vdim
+        return [self.w_in.shape[0], self.channels, hv, 3 * hv, self.o.shape[0]]
+
+    def forward(self, x, batch, cache):
+        p = ops.linear(x, self.w_in)
+        tails = cache.state[:, self.matrix_floats:] if self.taps > 1 else None
+        c = ops.conv_silu(p, 0, self.channels, self.conv_w, tails, batch)
+        gd = self.kv_heads * self.dim
+        y = ops.delta_scan("gated", batch, cache.state, (c, 0), (c, gd), (c, 2 * gd), (p, self.at_g), (p, self.at_a),
+                           (p, self.at_b), self.dt_bias, None, self.A_log, self.norm, False,
+                           self.heads, self.kv_heads, self.dim, self.vdim, self.eps,
+                           decay_per_head=True, gate_act="silu")
+        return ops.linear(y, self.o)

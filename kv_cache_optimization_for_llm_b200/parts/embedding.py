@@ -29,6 +29,30 @@ class TokenEmbedding(Part):
         return ops.embed_gather(self.table, batch.token_ids, batch.status, batch.sampled)
 
 
+@register("embedding", "normed_token_embedding")
+class NormedTokenEmbedding(TokenEmbedding):
+    """``residual[t] = rmsnorm(table[token[t]]) * weight``: the looked-up row passes an RMS norm (float32,
+    eps inside the root) before it starts the residual stream.  params: vocab_size, hidden_size, eps."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        return {"table": WeightSpec((params["vocab_size"], params["hidden_size"]), "matrix"),
+                "norm": WeightSpec((params["hidden_size"],), "vector")}
+
+    @classmethod
+    def kernel_modules(cls, params, dtype):
+        return ("elementwise", "rowwise")
+
+    def __init__(self, params, weights, ctx):
+        super().__init__(params, weights, ctx)
+        self.norm_weight, self.eps = weights["norm"], float(params["eps"])
+
+    def forward(self, batch):
+        import torch
+        rows = ops.embed_gather(self.table, batch.token_ids, batch.status, batch.sampled)
+        return ops.join_norm(rows, None, "rms", self.norm_weight, self.eps, torch.float32, compute_dtype=self.ctx.dtype)
+
+
 @register("head", "linear_head")
 class LinearHead(Part):
     """``logits = x . W^T`` in float32 output, W either its own tensor or the embedding

@@ -21,7 +21,7 @@ class RMSNorm(Part):
 
     @classmethod
     def kernel_modules(cls, params, dtype):
-        return ("elementwise",)      # the general kernel (rowwise) is loaded at first use, if a branch ever hands it a post norm
+        return ("elementwise",)      # the general kernels (rowwise) are loaded at first use, if a branch ever hands it a post norm or several summands
 
     def __init__(self, params, weights, ctx):
         super().__init__(params, weights, ctx)
@@ -47,6 +47,10 @@ class RMSNorm(Part):
         if isinstance(delta, ops.PostNormed):
             # a branch whose output passes a norm of its own first: the general kernel takes it in
             return ops.add_norm(residual, delta, "rms", self.weight, self.eps, self.ctx.dtype, rows)
+        if isinstance(delta, ops.PendingSum):
+            # several summands at once (two branches of a layer, what the start of a pass adds)
+            return ops.join_norm(residual, delta, "rms", self.weight, self.eps, self.ctx.dtype, rows,
+                                 compute_dtype=self.ctx.dtype)
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.ctx.dtype, rows)
 
 
@@ -94,4 +98,7 @@ class LayerNorm(Part):
     def forward(self, residual, delta=None, rows=None, lazy=False):
         if isinstance(delta, ops.Folded):
             delta = None        # that branch has added its output to the residual itself
+        if isinstance(delta, ops.PendingSum):
+            return ops.join_norm(residual, delta, self.norm_kind, self.weight, self.eps, self.ctx.dtype, rows,
+                                 compute_dtype=self.ctx.dtype)
         return ops.add_norm(residual, delta, self.norm_kind, self.weight, self.eps, self.ctx.dtype, rows)

@@ -5,7 +5,7 @@ from __future__ import annotations
 
 from typing import Dict
 
-FAMILIES = ("embedding", "mixer", "feed_forward", "norm", "position", "block", "head")
+FAMILIES = ("embedding", "mixer", "feed_forward", "norm", "position", "block", "head", "stream")
 _REG: Dict[str, Dict[str, type]] = {f: {} for f in FAMILIES}
 
 
@@ -35,4 +35,5 @@ def known(family: str):
 
 
 def _load_builtin() -> None:
-    from . import attention, block, delta_rule, embedding, feed_forward, latent_attention, norm, position  # noqa: F401
+    from . import (attention, block, delta_rule, embedding, experts, feed_forward, latent_attention, norm,  # noqa: F401
+                   position, stream, window_attention)
