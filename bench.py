@@ -422,6 +422,23 @@ def rezusun_config(z):
             "max_position_embeddings": CONTEXT_LEN}
 
 
+def solulix_config(z, window=1024, keep_first=64):
+    """Six layers at the comparison's sizes: attention (heads of 64, a quarter as many key/value heads, four taps, a
+    window of 1024 tokens that keeps the first 64) and the gated delta rule (heads of 64 x 64) in turn; dense
+    feed-forwards of the same width as Llama's, and on every third layer 16 experts of an eighth of that width of
+    which a token uses two, two identity experts and a shared expert of a quarter."""
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 8}, "shared": {"ff": z["ff"] // 4},
+           "router": {"experts": 16, "identity": 2, "top": 2, "scale": 2.0}}
+    att = {"heads": z["heads"], "kv_heads": z["heads"] // 4, "dim": 64, "vdim": 64, "conv": 4, "scale": 0.125,
+           "mask": {"size": window, "keep_first": keep_first}}
+    dlt = {"heads": z["heads"], "kv_heads": z["heads"] // 4, "dim": 64, "vdim": 64, "conv": 4}
+    kinds = [("attention", att, dense), ("attention", att, moe), ("delta", dlt, dense)]
+    return {"architecture": "Solulix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "layers": [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": kinds[i % 3][2]} for i in range(z["layers"])],
+            "max_position_embeddings": CONTEXT_LEN}
+
+
 def llama_config_like(z):
     cfg = dict(LLAMA_1B)
     cfg.update(hidden_size=z["width"], intermediate_size=z["ff"], vocab_size=z["vocab"], num_hidden_layers=z["layers"],
@@ -503,6 +520,71 @@ def measure_design(config_dict, decode_batch=8, decode_batch_ops=64):
     return out
 
 
+def run_compare_solulix(size):
+    """The Solulix design beside Llama at equal width, depth, feed-forward and vocabulary."""
+    z = COMPARE_SIZES[size]
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    w0 = time.perf_counter()
+    log(f"{size}: Llama")
+    llama = measure_design(llama_config_like(z))
+    log(f"{size}: Solulix")
+    window, keep = 1024, 64
+    sol = measure_design(solulix_config(z, window, keep))
+    w1 = time.perf_counter()
+    sampler.stop()
+    T, R, ctx = PREFILL_TOKENS, 64, PROMPT_LEN
+    pairs = T * (T + 1) // 2
+    # (query, key) pairs that the window and the kept first tokens leave of a T-token prompt
+    seen = sum(min(i + 1, window) + max(0, min(keep, i + 1 - window)) for i in range(T))
+    H, G, W = z["heads"], z["heads"] // 4, z["width"]
+    channels = (H + 2 * G) * 64
+    n_cols = 16 * (z["ff"] // 8) + z["ff"] // 4
+
+    def per_launch(d, phase, key, *names):
+        for name in names:
+            n, ms = d[phase][key].get(name, (0, 0.0))
+            if n:
+                return ms / n
+        return None
+
+    def frac(work, ms, peak_per_s):
+        return None if not ms else round(work / (ms * 1e-3) / peak_per_s, 4)
+    tensor, hbm, fma = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9, FP32_FMA_TFLOPS_NOMINAL * 1e12
+    kernels = {
+        "llama flash_attention, 2048 tokens (of the measured bf16 peak)": frac(
+            pairs * 4 * H * 64, per_launch(llama, "prefill_2048", "operators", "paged_flash_attention"), tensor),
+        "solulix attention, 2048 tokens (of the measured bf16 peak)": frac(
+            seen * 4 * H * 64, per_launch(sol, "prefill_2048", "operators", "flash_attention_rows", "window_attention"), tensor),
+        "llama decode_attention_mma, batch 64 (of the measured copy peak)": frac(
+            R * ctx * 2 * G * 64 * 2, per_launch(llama, "decode_b64", "operators_launched", "decode_attention_mma"), hbm),
+        "solulix window_attention, batch 64 (of the measured copy peak)": frac(
+            R * min(ctx, window + keep) * 2 * G * 64 * 2, per_launch(sol, "decode_b64", "operators_launched", "window_attention"), hbm),
+        "llama rope_kv_write, 2048 tokens (of the measured copy peak)": frac(
+            T * (2 * channels + 2 * G * 64) * 2, per_launch(llama, "prefill_2048", "operators", "rope_kv_write"), hbm),
+        "solulix conv_silu, 2048 tokens (of the measured copy peak)": frac(
+            T * 2 * channels * 2, per_launch(sol, "prefill_2048", "operators", "conv_silu"), hbm),
+        "solulix kv_rows_append, 2048 tokens (of the measured copy peak)": frac(
+            T * 2 * 2 * G * 64 * 2, per_launch(sol, "prefill_2048", "operators", "kv_rows_append"), hbm),
+        "solulix delta_scan, 2048 tokens (of the nominal fp32 FMA peak)": frac(
+            T * H * 64 * 64 * 10, per_launch(sol, "prefill_2048", "operators", "delta_scan"), fma),
+        "solulix delta_scan, batch 64 (of the measured copy peak)": frac(
+            2 * R * H * 64 * 64 * 4, per_launch(sol, "decode_b64", "operators_launched", "delta_scan"), hbm),
+        "llama add_rmsnorm, 2048 tokens (of the measured copy peak)": frac(
+            T * W * 12, per_launch(llama, "prefill_2048", "operators", "add_rmsnorm"), hbm),
+        "solulix join_norm, 2048 tokens (of the measured copy peak)": frac(
+            T * W * 14, per_launch(sol, "prefill_2048", "operators", "join_norm"), hbm),
+        "solulix expert_act, 2048 tokens (of the measured copy peak)": frac(
+            T * n_cols * 4, per_launch(sol, "prefill_2048", "operators", "expert_act"), hbm),
+        "solulix route, 2048 tokens (of the nominal fp32 FMA peak)": frac(
+            T * 18 * W * 2, per_launch(sol, "prefill_2048", "operators", "route"), fma),
+    }
+    return {"compare": size, "design": "solulix", "sizes": z, "window": window, "keep_first": keep, "dtype": "bf16",
+            "data": "synthetic", "peaks": pk, "llama": llama, "solulix": sol, "kernel_roofline_fractions": kernels,
+            "clocks": sampler.summary(list(_compare_windows) or [(w0, w1)])}
+
+
 def run_compare(size):
     """The Rezusun design beside Llama at equal width, depth, feed-forward and vocabulary."""
     z = COMPARE_SIZES[size]
@@ -576,13 +658,16 @@ def main():
                     help="the serving workloads measured beside the headline (3B continuous batching, 8B under a "
                          "pool that is too small); one name runs that workload alone and prints its own JSON line")
     ap.add_argument("--compare", default=None, choices=sorted(COMPARE_SIZES),
-                    help="instead of the headline: prefill and decode of the Rezusun design beside a Llama model of "
+                    help="instead of the headline: prefill and decode of another design (--design) beside a Llama model of "
                          "equal width, depth, feed-forward and vocabulary (random weights), with the time of every "
                          "operator and roofline fractions of the designs' own kernels; prints its own JSON line")
+    ap.add_argument("--design", default="rezusun", choices=["rezusun", "solulix"],
+                    help="with --compare: which design stands beside Llama")
     args = ap.parse_args()
 
     if args.compare:
-        print(json.dumps(run_compare(args.compare)), flush=True)
+        result = run_compare_solulix(args.compare) if args.design == "solulix" else run_compare(args.compare)
+        print(json.dumps(result), flush=True)
         return 0
     if args.impl == "reference":
         # upstream's own engine, unmodified, driven through its standard input and output

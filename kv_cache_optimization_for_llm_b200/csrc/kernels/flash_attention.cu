@@ -64,14 +64,23 @@ template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
 
 struct TileDesc { int req, t0, n_tok, pad; };
 
-template <int D, int NW>
+// What the kernel below takes beyond the plain causal (windowed) mask when it is built with EXT:
+//   kv_row_stride  elements from one cached token to the next of the same page and head (pools whose
+//                  rows hold a token's key and value side by side; k_pages and v_pages then point at
+//                  the first key and at the first value of the same pool)
+//   keep_first     with a window: keys below it are seen whatever the window; the walk over the key
+//                  tiles then starts with the tiles that hold them
+//   one_more       the softmax's denominator counts one more key, of score 0 and without a value
+struct MaskExt { int kv_row_stride, keep_first, one_more; };
+
+template <int D, int NW, bool EXT>
 __global__ void __launch_bounds__(NW * 32, (D == 64 ? 16 : 8) / NW)
 paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row_stride,
                              const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
                              const int* __restrict__ block_table, int max_pages, int page_shift, int num_pages,
                              const int* __restrict__ positions, const TileDesc* __restrict__ tiles,
                              __nv_bfloat16* __restrict__ out, int nq, int nkv, int G, int gp_shift,
-                             float scale_log2, int window, int* status) {
+                             float scale_log2, int window, int* status, MaskExt ext) {
   constexpr int BM = NW * 16;       // query rows of this block
   constexpr int kThreads = NW * 32;
   constexpr int CPK = D / 8;        // 16-byte chunks per row
@@ -103,6 +112,12 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
   const int k_hi = pos_last + 1;                                    // keys [.., k_hi) are read
   const int k_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
   const int first_tile = k_lo / BN, last_tile = (k_hi - 1) / BN;
+  // EXT: the tiles in front of the window's first that hold kept first keys are walked first
+  const int keep = (EXT && window > 0) ? ext.keep_first : 0;
+  const int keep_tiles = EXT ? min((keep + BN - 1) / BN, first_tile) : 0;
+  const int n_walk = keep_tiles + last_tile - first_tile + 1;
+  const int kv_stride = EXT ? ext.kv_row_stride : D;
+  auto tile_at = [&](int idx) { return idx < keep_tiles ? idx : first_tile + idx - keep_tiles; };
 
   // ---- loaders ------------------------------------------------------------------
   auto load_q = [&]() {
@@ -126,7 +141,7 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
     unsigned char* vd = v_s + buf * BN * D * 2;
     const int key = tid / TPK, part0 = (tid % TPK) * CPT;
     const int j = t * BN + key;
-    bool ok = j < k_hi && j >= k_lo;
+    bool ok = j < k_hi && (j >= k_lo || j < keep);
     size_t off = 0;
     if (ok) {
       const int lp = j >> page_shift;
@@ -135,7 +150,7 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
         atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
         ok = false;
       } else {
-        off = ((((size_t)page * nkv + hk) << page_shift) + (j & page_mask)) * D;
+        off = ((((size_t)page * nkv + hk) << page_shift) + (j & page_mask)) * kv_stride;
       }
     }
 #pragma unroll
@@ -147,7 +162,7 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
   };
 
   load_q();
-  load_kv(first_tile, 0);
+  load_kv(tile_at(0), 0);
   cp_async_commit();
 
   // ---- per-thread state: rows r0 = warp*16 + lane/4 and r0 + 8 ---------------------
@@ -159,17 +174,18 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
   const int r0 = warp * 16 + (lane >> 2);
   int pos_r[2], lo_r[2];
 
-  for (int t = first_tile; t <= last_tile; ++t) {
-    const int buf = (t - first_tile) & 1;
-    if (t < last_tile) {
-      load_kv(t + 1, buf ^ 1);
+  for (int idx = 0; idx < n_walk; ++idx) {
+    const int t = tile_at(idx);
+    const int buf = idx & 1;
+    if (idx + 1 < n_walk) {
+      load_kv(tile_at(idx + 1), buf ^ 1);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (t == first_tile) {
+    if (idx == 0) {
       // query fragments stay in registers for the whole walk
 #pragma unroll
       for (int kk = 0; kk < KSTEPS; ++kk)
@@ -204,8 +220,8 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
     // window needs no per-element test; the tiles on the diagonal and at the window's edge do.
     const int kbase = t * BN + ((lane & 3) << 1);
     float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
-    const bool full = (t * BN + BN - 1 <= min(pos_r[0], pos_r[1])) && (t * BN >= max(lo_r[0], lo_r[1])) &&
-                      pos_r[0] >= 0 && pos_r[1] >= 0;
+    const bool full = (t * BN + BN - 1 <= min(pos_r[0], pos_r[1])) &&
+                      (t * BN >= max(lo_r[0], lo_r[1]) || t * BN + BN - 1 < keep) && pos_r[0] >= 0 && pos_r[1] >= 0;
     if (__all_sync(0xffffffffu, full)) {
 #pragma unroll
       for (int n = 0; n < BN / 8; ++n) {
@@ -222,7 +238,7 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
         for (int e = 0; e < 4; ++e) {
           const int j = kbase + n * 8 + (e & 1);
           const int rr = e >> 1;
-          const bool ok = j <= pos_r[rr] && j >= lo_r[rr];
+          const bool ok = j <= pos_r[rr] && (j >= lo_r[rr] || j < keep);
           s[n][e] = ok ? s[n][e] * scale_log2 : -CUDART_INF_F;
           mx[rr] = fmaxf(mx[rr], s[n][e]);
         }
@@ -282,6 +298,8 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
     const int row = r0 + rr * 8;
     const int ti = row >> gp_shift, hi = row & (gp - 1);
     if (ti >= tile.n_tok || hi >= G) continue;
+    if (EXT && ext.one_more)      // the one more key: score 0, which is 0 in units of log2 too; no value
+      l_run[rr] += (m_run[rr] == -CUDART_INF_F) ? 1.f : exp2f(-m_run[rr]);
     const float inv = l_run[rr] > 0.f ? 1.0f / l_run[rr] : 0.f;
     __nv_bfloat16* dst = out + ((size_t)(tile.t0 + ti) * nq + hk * G + hi) * D + ((lane & 3) << 1);
 #pragma unroll
@@ -1152,23 +1170,23 @@ int launch_ws(const void* q, int q_row_stride, const void* k_pages, const void* 
 
 }  // namespace tc5
 
-template <int D, int NW>
+template <int D, int NW, bool EXT = false>
 int launch(const void* q, int q_row_stride, const void* k_pages, const void* v_pages, const int* block_table,
            int max_pages, int page_shift, int num_pages, const int* positions, const void* tiles, int num_tiles,
            void* out, int nq, int nkv, int G, int gp_shift, float scale, int window, int* status,
-           cudaStream_t stream) {
+           cudaStream_t stream, MaskExt ext = MaskExt{D, 0, 0}) {
   constexpr int BM = NW * 16;
   const size_t smem = (size_t)BM * D * 2 + 4 * (size_t)BN * D * 2 + BM * sizeof(int);
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(paged_flash_attention_kernel<D, NW>,
+    cudaError_t e = cudaFuncSetAttribute(paged_flash_attention_kernel<D, NW, EXT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(num_tiles, nkv);
-  kvb_launch(paged_flash_attention_kernel<D, NW>, grid, dim3(NW * 32), smem, stream, (const __nv_bfloat16*)q,
+  kvb_launch(paged_flash_attention_kernel<D, NW, EXT>, grid, dim3(NW * 32), smem, stream, (const __nv_bfloat16*)q,
              q_row_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, max_pages,
              page_shift, num_pages, positions, (const TileDesc*)tiles, (__nv_bfloat16*)out, nq, nkv, G, gp_shift,
-             scale * 1.4426950408889634f, window, status);
+             scale * 1.4426950408889634f, window, status, ext);
   return kvb_launch_result();
 }
 
@@ -1236,4 +1254,34 @@ KVB_EXPORT int kvb_paged_flash_attention(const void* q, int q_row_stride, const 
   if (d == 64) { if (wide) KVB_FA(64, 8); KVB_FA(64, 4); }
   if (wide) KVB_FA(128, 8);
   KVB_FA(128, 4);
+}
+
+
+// The mma.sync form above for mixers whose mask and softmax go beyond the plain causal window (see MaskExt):
+// key and value of a token lie side by side in one pool, `pages` [num_pages, nkv, page_size, 2 d]; query i sees
+// key j when j <= i and (i - j < window or j < keep_first) (window 0: every key up to i); with one_more the
+// softmax's denominator is 1 + sum exp(s).  Key and value size are both d (64 or 128).  wide: 0 or 1 as above.
+KVB_EXPORT int kvb_paged_flash_attention_rows(const void* q, int q_row_stride, const void* pages, const int* block_table,
+                                              int max_pages, int page_size, int num_pages, const int* positions,
+                                              const void* tiles, int num_tiles, int wide, void* out, int nq, int nkv,
+                                              int d, float scale, int window, int keep_first, int one_more, int* status,
+                                              cudaStream_t stream) {
+  if (num_tiles <= 0) return 0;
+  if (nkv < 1 || nq % nkv || window < 0 || keep_first < 0) return KVB_ERR_BAD_SIZE;
+  const int G = nq / nkv;
+  if (!kvb_flash_attention_supported(d, G, page_size) || nkv > 65535) return KVB_ERR_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_row_stride & 7) || (reinterpret_cast<uintptr_t>(pages) & 15))
+    return KVB_ERR_ALIGN;
+  int gp_shift = 0;
+  while ((1 << gp_shift) < G) ++gp_shift;
+  const int page_shift = log2_exact(page_size);
+  if (wide && (128 >> gp_shift) < 1) return KVB_ERR_BAD_SIZE;
+  const MaskExt ext{2 * d, keep_first, one_more};
+  const void* values = static_cast<const __nv_bfloat16*>(pages) + d;
+#define KVB_FA_EXT(D, NW)                                                                                              \
+  return (launch<D, NW, true>(q, q_row_stride, pages, values, block_table, max_pages, page_shift, num_pages, positions, \
+                              tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, window, status, stream, ext))
+  if (d == 64) { if (wide) KVB_FA_EXT(64, 8); KVB_FA_EXT(64, 4); }
+  if (wide) KVB_FA_EXT(128, 8);
+  KVB_FA_EXT(128, 4);
 }

@@ -669,6 +669,37 @@ def window_attention(q: torch.Tensor, q_off: int, pages: torch.Tensor, block_tab
     return out
 
 
+def flash_attention_rows_supported(dk: int, dv: int, group: int, page_size: int, dtype: torch.dtype) -> bool:
+    """Whether the tensor-core form of :func:`window_attention` takes these sizes: bfloat16, key and value
+    size equal and 64 or 128, pages of a power of two."""
+    return dtype == torch.bfloat16 and dk == dv and flash_attention_supported(dk, group, page_size)
+
+
+def flash_attention_rows(q: torch.Tensor, pages: torch.Tensor, block_table, batch, heads: int, kv_heads: int, d: int,
+                         scale: float, window: int, keep_first: int, one_more: bool,
+                         wide: Optional[bool] = None) -> torch.Tensor:
+    """:func:`window_attention` on tensor cores for steps with runs of query tokens (bfloat16, key and value
+    size ``d`` both): tiles of 64 or 128 (token, head of a group) rows against tiles of 64 keys, the tiles that
+    hold kept first keys in front of the window's own.  Queries at ``q[:, : heads * d]``."""
+    _need_cuda(q, pages)
+    assert q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and pages.is_contiguous() and q.stride(1) == 1
+    assert tuple(pages.shape[1:]) == (kv_heads, pages.shape[2], 2 * d)
+    T = q.shape[0]
+    group = heads // kv_heads
+    if wide is None:
+        wide = FLASH_WIDE and (T // flash_tokens_per_tile(group, True)) * kv_heads >= (2 if d == 64 else 1) * sm_count(q.device)
+    tiles = flash_tiles(batch, group, bool(wide))
+    out = new((T, heads * d), q.dtype, q.device)
+    rc = lib("flash_attention").kvb_paged_flash_attention_rows(
+        _p(q), c_int(q.stride(0)), _p(pages), _p(block_table), c_int(block_table.shape[1]), c_int(pages.shape[2]),
+        c_int(pages.shape[0]), _p(batch.positions), _p(tiles), c_int(tiles.shape[0]), c_int(1 if wide else 0), _p(out),
+        c_int(heads), c_int(kv_heads), c_int(d), c_float(scale), c_int(int(window or 0)), c_int(int(keep_first or 0)),
+        c_int(1 if one_more else 0), _p(batch.status), _stream())
+    _check(rc, "flash_attention_rows")
+    choices["flash_attention_rows"] += 1
+    return out
+
+
 # ------------------------------------------------------------------ routed experts
 
 def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, experts: int, identity: int, top: int,

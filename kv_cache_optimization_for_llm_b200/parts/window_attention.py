@@ -24,6 +24,9 @@ class ConvWindowAttention(Part):
     [k | v].  Query i sees key j when ``j <= i and (i - j < window or j < keep_first)`` (``window`` None:
     every key up to i); scores are ``(q . k) * scale``; with ``one_more`` the softmax's denominator is
     ``1 + sum exp(s)``.  Query head h reads key/value head ``h // (heads / kv_heads)``.  Then W_o.
+    Kernels: the general one (float32 arithmetic, any sizes, chunks of keys by absolute position) for
+    float32, for steps of single tokens and for sizes the other refuses; for bfloat16 steps with runs
+    of tokens and key and value size both 64 or 128 the tensor-core kernel of prompt portions.
     params: hidden_size, heads, kv_heads, dim, vdim, conv, scale, window, keep_first, one_more."""
 
     @classmethod
@@ -35,8 +38,10 @@ class ConvWindowAttention(Part):
 
     @classmethod
     def kernel_modules(cls, params, dtype):
-        return ("window_attention", "delta_rule") + (("gemm_f32",) if dtype == torch.float32
-                                                      else ("gemm_bf16", "gemm_bf16_wide"))
+        mods = ["window_attention", "delta_rule"]
+        if dtype == torch.bfloat16 and params["dim"] == params["vdim"] and params["dim"] in (64, 128):
+            mods.append("flash_attention")
+        return tuple(mods) + (("gemm_f32",) if dtype == torch.float32 else ("gemm_bf16", "gemm_bf16_wide"))
 
     def __init__(self, params, weights, ctx):
         super().__init__(params, weights, ctx)
@@ -69,12 +74,27 @@ class ConvWindowAttention(Part):
     def activation_widths(self):
         return [self.channels, self.channels, self.heads * self.vdim, self.o.shape[0]]
 
+    def _on_tensor_cores(self, page_size):
+        return ops.flash_attention_rows_supported(self.dim, self.vdim, self.heads // self.kv_heads, page_size, self.ctx.dtype)
+
+    def query_tile_heights(self):
+        """Tokens per tile of the tensor-core kernel for prompt portions (bfloat16, key and value size
+        64 or 128): the step's batch lays the tiles out for them."""
+        if self.ctx.dtype != torch.bfloat16 or self.dim != self.vdim or self.dim not in (64, 128):
+            return []
+        g = self.heads // self.kv_heads
+        return [ops.flash_tokens_per_tile(g, False), ops.flash_tokens_per_tile(g, True)]
+
     def forward(self, x, batch, cache):
         p = ops.linear(x, self.qkv)
         c = ops.conv_silu(p, 0, self.channels, self.conv_w, cache.state, batch, act="none")
         table = batch.block_tables[cache.group]
         if cache.write:
             ops.kv_rows_append(c, self.k_off, self.v_off, cache.k, table, batch, self.kv_heads, self.dim, self.vdim)
-        a = ops.window_attention(c, 0, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.vdim,
-                                 self.scale, self.window or 0, self.keep_first, self.one_more)
+        if not batch.decode_only and self._on_tensor_cores(cache.page_size) and c.stride(0) % 8 == 0:
+            a = ops.flash_attention_rows(c, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.scale,
+                                         self.window or 0, self.keep_first, self.one_more)
+        else:
+            a = ops.window_attention(c, 0, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.vdim,
+                                     self.scale, self.window or 0, self.keep_first, self.one_more)
         return ops.linear(a, self.o)
