@@ -388,6 +388,129 @@ __global__ void conv_silu_kernel(const T* __restrict__ in, int ld, const float* 
   out[(size_t)t * C + c] = from_f32<T>(act == 0 ? acc / (1.0f + expf(-acc)) : acc);
 }
 
+// The same for rows of channels that are multiples of 16 bytes: a thread takes VEC consecutive channels of one
+// token (one 16-byte load per tap).  It can also write the convolved keys and values of an attention mixer into
+// the request's pages, whose rows hold [key | value] per token and key/value head (`ap.pages` not null): the
+// channels from k_off on are kv_heads keys of Dk, those from v_off on kv_heads values of Dv.
+struct AppendArgs {
+  void* pages; const int* block_table; int max_pages, page_size, num_pages, k_off, v_off, kv_heads, Dk, Dv; int* status;
+};
+
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* x) {
+    const float4 u = *reinterpret_cast<const float4*>(p); x[0] = u.x; x[1] = u.y; x[2] = u.z; x[3] = u.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* x) {
+    *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+  }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* x) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { x[2 * e] = __uint_as_float(w[e] << 16); x[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u); }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* x) {
+    unsigned w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      __nv_bfloat162 v = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
+      w[e] = *reinterpret_cast<unsigned*>(&v);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+// TAPS > 0: the number of taps, known when the kernel is built; the thread's VEC x TAPS weights are then fetched with
+// 16-byte loads into registers.  TAPS 0: any number, the weights fetched one by one.
+template <typename T, int TAPS>
+__global__ void conv_vec_kernel(const T* __restrict__ in, int ld, const float* __restrict__ w, int taps,
+                                const float* __restrict__ tails, long long slot_stride, T* __restrict__ out, int C,
+                                int T_, const int* __restrict__ positions, const int* __restrict__ token_req,
+                                const int* __restrict__ q_start, const int* __restrict__ req_start,
+                                const int* __restrict__ slots, int act, AppendArgs ap) {
+  constexpr int VEC = Vec16<T>::N;
+  pdl_trigger();
+  pdl_wait();
+  const int groups = C / VEC;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)T_ * groups) return;
+  const int t = (int)(idx / groups), c = (int)(idx - (long long)t * groups) * VEC;
+  const int pos = positions[t], r = token_req[t];
+  const int start = req_start[r], row0 = q_start[r];
+  const float* tail = tails + (size_t)slots[r] * slot_stride;
+  float acc[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+  if (TAPS > 0) {
+    constexpr int NT = TAPS > 0 ? TAPS : 1;
+    float wv[VEC * NT];                       // channel e's taps at wv[e * NT ..]; c * NT floats is a multiple of 16 bytes
+#pragma unroll
+    for (int i = 0; i < VEC * NT; i += 4) {
+      const float4 u = *reinterpret_cast<const float4*>(w + (size_t)c * NT + i);
+      wv[i] = u.x; wv[i + 1] = u.y; wv[i + 2] = u.z; wv[i + 3] = u.w;
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const int sp = pos - (NT - 1) + j;
+      float x[VEC];
+      if (sp >= start) {
+        Vec16<T>::load(in + (size_t)(row0 + sp - start) * ld + c, x);
+      } else if (sp >= 0) {
+        const float* tp = tail + (size_t)(sp - (start - (NT - 1))) * C + c;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x[e] = tp[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x[e] = 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = fmaf(wv[e * NT + j], x[e], acc[e]);
+    }
+  } else {
+    for (int j = 0; j < taps; ++j) {
+      const int sp = pos - (taps - 1) + j;
+      if (sp < 0) continue;
+      float x[VEC];
+      if (sp >= start) {
+        Vec16<T>::load(in + (size_t)(row0 + sp - start) * ld + c, x);
+      } else {
+        const float* tp = tail + (size_t)(sp - (start - (taps - 1))) * C + c;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x[e] = tp[e];
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = fmaf(w[(size_t)(c + e) * taps + j], x[e], acc[e]);
+    }
+  }
+  if (act == 0) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = acc[e] / (1.0f + expf(-acc[e]));
+  }
+  Vec16<T>::store(out + (size_t)t * C + c, acc);
+  if (ap.pages != nullptr && c >= ap.k_off) {
+    const bool is_v = c >= ap.v_off;
+    const int width = is_v ? ap.Dv : ap.Dk;
+    const int rel = c - (is_v ? ap.v_off : ap.k_off);
+    const int g = rel / width, i = rel - g * width;
+    if (g < ap.kv_heads) {
+      const int lp = pos / ap.page_size;
+      const int page = lp < ap.max_pages ? ap.block_table[(size_t)r * ap.max_pages + lp] : -1;
+      if (page < 0 || page >= ap.num_pages) {
+        atomicCAS(ap.status, 0, KVB_STATUS_UNMAPPED_PAGE);
+      } else {
+        T* row = static_cast<T*>(ap.pages) +
+                 (((size_t)page * ap.kv_heads + g) * ap.page_size + (pos % ap.page_size)) * (ap.Dk + ap.Dv);
+        Vec16<T>::store(row + (is_v ? ap.Dk : 0) + i, acc);
+      }
+    }
+  }
+}
+
 // After the convolution: the request's tail becomes the last taps - 1 inputs up to the end of the
 // step's run (older ones move up when the run is shorter than the tail).
 constexpr int kMaxTail = 15;
@@ -412,17 +535,47 @@ __global__ void conv_tail_kernel(const T* __restrict__ in, int ld, int taps, flo
     if (j < taps - 1) tail[(size_t)j * C + c] = keep[j];
 }
 
+// append: null, or where the convolved keys and values of an attention mixer go as well (see AppendArgs; only rows
+// of whole 16-byte groups can: the launcher refuses otherwise and the caller writes them with a kernel of its own).
 // in: [T, >= C] with row stride ld; w [C, taps] float32; tails: the tail of slot 0, slot_stride
 // floats from slot to slot, each [taps - 1, C]; out [T, C] dense.  act: 0 SiLU behind the sum, 1 the
 // bare sum.  Refuses taps > 16.
 KVB_EXPORT int kvb_conv_silu(const void* in, int ld, const float* w, int taps, float* tails, long long slot_stride,
                              void* out, int C, int T_, int R, const int* positions, const int* token_req,
                              const int* q_start, const int* req_start, const int* ctx_len, const int* slots,
-                             int act, int dtype, cudaStream_t stream) {
+                             int act, const AppendArgs* append, int dtype, cudaStream_t stream) {
   if (T_ <= 0 || R <= 0) return 0;
   if (taps < 1 || taps - 1 > kMaxTail || C < 1 || act < 0 || act > 1) return KVB_ERR_BAD_SIZE;
   const int threads = 128;
   const int by = (C + threads - 1) / threads;
+  // rows of whole 16-byte groups: the vector form, which can also write keys and values into their pages
+  const int vec = dtype == KVB_F32 ? 4 : 8;
+  AppendArgs ap = {};
+  if (append != nullptr) ap = *append;
+  const bool aligned = C % vec == 0 && ld % vec == 0 && ((uintptr_t)in % 16) == 0 && ((uintptr_t)out % 16) == 0;
+  if (ap.pages != nullptr &&
+      !(aligned && ap.Dk % vec == 0 && ap.Dv % vec == 0 && ap.k_off % vec == 0 && ap.v_off % vec == 0 &&
+        ((uintptr_t)ap.pages % 16) == 0 && ap.kv_heads >= 1 && ap.page_size >= 1 &&
+        ap.k_off + ap.kv_heads * ap.Dk <= ap.v_off && ap.v_off + ap.kv_heads * ap.Dv <= C))
+    return KVB_ERR_BAD_SIZE;
+  if (aligned) {
+    const long long units = (long long)T_ * (C / vec);
+    const bool w16 = ((uintptr_t)w % 16) == 0;
+#define KVB_CONV(TAPS)                                                                                                  \
+  kvb_launch(conv_vec_kernel<T, TAPS>, dim3((unsigned)((units + 255) / 256)), dim3(256), 0, stream, (const T*)in, ld, w, \
+             taps, (const float*)tails, slot_stride, (T*)out, C, T_, positions, token_req, q_start, req_start, slots, act, ap)
+    KVB_DISPATCH_DTYPE(dtype, T, {
+      if (taps == 2 && w16) KVB_CONV(2);
+      else if (taps == 3 && w16) KVB_CONV(3);
+      else if (taps == 4 && w16) KVB_CONV(4);
+      else KVB_CONV(0);
+      if (taps > 1)
+        kvb_launch(conv_tail_kernel<T>, dim3(R, by), dim3(threads), 0, stream, (const T*)in, ld, taps, tails, slot_stride,
+                   C, q_start, req_start, ctx_len, slots);
+    });
+#undef KVB_CONV
+    return kvb_launch_result();
+  }
   KVB_DISPATCH_DTYPE(dtype, T, {
     kvb_launch(conv_silu_kernel<T>, dim3(T_, by), dim3(threads), 0, stream, (const T*)in, ld, w, taps,
                (const float*)tails, slot_stride, (T*)out, C, positions, token_req, q_start, req_start, slots, act);

@@ -1,7 +1,7 @@
 // A feed-forward made of many small experts of which every token uses a few.
 //
-//   * route_kernel: the router.  One warp per token: logits z = W_r h in float32 (W_r float32, h as
-//     stored), scores s = softmax(z) over all experts, the `top` experts with the largest s + correction
+//   * route_kernel: the router.  A block per up to eight tokens: logits z = W_r h in float32 (W_r float32, h as
+//     stored; or handed in by the caller, who made them with a product of float32 sums), scores s = softmax(z) over all experts, the `top` experts with the largest s + correction
 //     (ties go to the lower index), their weights s / (sum of the chosen s + 1e-20) * scale.  It
 //     leaves a dense table gate[t, e] (0 for an expert that was not chosen) and, for the last
 //     `identity` experts, which have no matrices and hand their input on, the sum of their weights.
@@ -17,97 +17,134 @@
 #include <math_constants.h>
 
 constexpr int kRouteWarps = 4;
+constexpr int kRouteTokens = 8;        // tokens a block routes at most: a router row is fetched once for all of them
 
+// A block takes `tb` consecutive tokens (1, 2, 4 or 8, as many as their inputs fit shared memory).  Logits: warp w
+// makes those of the experts e = w, w + 4, ...: its lanes walk the row of W_r once (lane l the columns l, l + 32, ...)
+// and keep one sum per token; the lanes' sums are then added across the warp.  A token's sums are taken in an order
+// that depends on K only.  Then warp w chooses for the tokens w, w + 4, ...
 template <typename T>
 __global__ void __launch_bounds__(kRouteWarps * 32)
-route_kernel(const T* __restrict__ h, int ld_h, const float* __restrict__ w_router, const float* __restrict__ correction,
-             float* __restrict__ gate, float* __restrict__ identity_weight, int T_, int K, int E, int n_identity, int top,
-             float scale) {
+route_kernel(const T* __restrict__ h, int ld_h, const float* __restrict__ w_router, const float* __restrict__ logits,
+             const float* __restrict__ correction, float* __restrict__ gate, float* __restrict__ identity_weight, int T_,
+             int K, int E, int n_identity, int top, float scale, int tb) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * kRouteWarps + warp;
-  if (t >= T_) return;
+  const int t0 = blockIdx.x * tb;
+  const int n_tok = min(tb, T_ - t0);
   const int n_all = E + n_identity;
-  float* x = smem + (size_t)warp * (K + 2 * n_all);     // the token's input, float32
-  float* s = x + K;                                     // scores
-  float* c = s + n_all;                                 // choice scores; -inf once chosen
-  for (int k = lane; k < K; k += 32) x[k] = to_f32(h[(size_t)t * ld_h + k]);
-  __syncwarp();
-  float zmax = -CUDART_INF_F;
-  for (int e = 0; e < n_all; ++e) {
-    const float* wr = w_router + (size_t)e * K;
-    float part = 0.f;
-    for (int k = lane; k < K; k += 32) part = fmaf(wr[k], x[k], part);
-    const float z = warp_sum(part);
-    if (lane == 0) s[e] = z;
-    zmax = fmaxf(zmax, z);
-  }
-  __syncwarp();
-  float sum = 0.f;
-  for (int e = lane; e < n_all; e += 32) {
-    const float v = expf(s[e] - zmax);
-    s[e] = v;
-    sum += v;
-  }
-  sum = warp_sum(sum);
-  __syncwarp();
-  for (int e = lane; e < n_all; e += 32) {
-    s[e] = s[e] / sum;
-    c[e] = s[e] + correction[e];
-    gate[(size_t)t * n_all + e] = 0.f;
-  }
-  __syncwarp();
-  // the chosen experts, one after the other; their indices end up in lane 0 .. top - 1's `mine`
-  int mine = -1;
-  float chosen_sum = 0.f;
-  for (int r = 0; r < top; ++r) {
-    float best = -CUDART_INF_F;
-    int at = 0x7fffffff;
-    for (int e = lane; e < n_all; e += 32)
-      if (c[e] > best) { best = c[e]; at = e; }       // ascending e: the lowest index among equals
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+  float* s_all = smem;                                  // [tb][n_all] logits, then scores
+  float* c_all = s_all + (size_t)tb * n_all;            // [tb][n_all] choice scores; -inf once chosen
+  float* x = c_all + (size_t)tb * n_all;                // [tb][K] the tokens' inputs, float32 (not with logits)
+  if (logits != nullptr) {
+    for (int i = threadIdx.x; i < n_tok * n_all; i += blockDim.x) s_all[i] = logits[(size_t)t0 * n_all + i];
+  } else {
+    for (int i = threadIdx.x; i < n_tok * K; i += blockDim.x) {
+      const int tt = i / K, k = i - tt * K;
+      x[i] = to_f32(h[(size_t)(t0 + tt) * ld_h + k]);
     }
-    if (at == 0x7fffffff) break;                      // fewer experts than `top`
-    if (lane == r % 32 && r < 32) mine = at;
-    chosen_sum += s[at];
-    __syncwarp();
-    if (lane == 0) c[at] = -CUDART_INF_F;
-    __syncwarp();
+    for (int i = threadIdx.x + n_tok * K; i < tb * K; i += blockDim.x) x[i] = 0.f;
+    __syncthreads();
+    for (int e = warp; e < n_all; e += kRouteWarps) {
+      const float* wr = w_router + (size_t)e * K;
+      float part[kRouteTokens];
+#pragma unroll
+      for (int tt = 0; tt < kRouteTokens; ++tt) part[tt] = 0.f;
+#pragma unroll 4
+      for (int k = lane; k < K; k += 32) {
+        const float wv = wr[k];
+#pragma unroll
+        for (int tt = 0; tt < kRouteTokens; ++tt)
+          if (tt < tb) part[tt] = fmaf(wv, x[tt * K + k], part[tt]);
+      }
+#pragma unroll
+      for (int tt = 0; tt < kRouteTokens; ++tt) {
+        if (tt >= tb) break;
+        const float z = warp_sum(part[tt]);
+        if (lane == 0) s_all[tt * n_all + e] = z;
+      }
+    }
   }
-  const float norm = scale / (chosen_sum + 1e-20f);
-  float idw = 0.f;
-  for (int r = 0; r < top && r < 32; ++r) {
-    const int e = __shfl_sync(0xffffffffu, mine, r);
-    if (e < 0) continue;
-    const float g = s[e] * norm;
-    if (lane == 0) gate[(size_t)t * n_all + e] = g;
-    if (e >= E) idw += g;
+  __syncthreads();
+  for (int tt = warp; tt < n_tok; tt += kRouteWarps) {
+    const int t = t0 + tt;
+    float* s = s_all + (size_t)tt * n_all;
+    float* c = c_all + (size_t)tt * n_all;
+    float zmax = -CUDART_INF_F;
+    for (int e = lane; e < n_all; e += 32) zmax = fmaxf(zmax, s[e]);
+    zmax = warp_max(zmax);
+    float sum = 0.f;
+    for (int e = lane; e < n_all; e += 32) {
+      const float v = expf(s[e] - zmax);
+      s[e] = v;
+      sum += v;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < n_all; e += 32) {
+      s[e] = s[e] / sum;
+      c[e] = s[e] + correction[e];
+      gate[(size_t)t * n_all + e] = 0.f;
+    }
+    __syncwarp();
+    // the chosen experts, one after the other; their indices end up in lane 0 .. top - 1's `mine`
+    int mine = -1;
+    float chosen_sum = 0.f;
+    for (int r = 0; r < top; ++r) {
+      float best = -CUDART_INF_F;
+      int at = 0x7fffffff;
+      for (int e = lane; e < n_all; e += 32)
+        if (c[e] > best) { best = c[e]; at = e; }       // ascending e: the lowest index among equals
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+      }
+      if (at == 0x7fffffff) break;                      // fewer experts than `top`
+      if (lane == r) mine = at;
+      chosen_sum += s[at];
+      __syncwarp();
+      if (lane == 0) c[at] = -CUDART_INF_F;
+      __syncwarp();
+    }
+    const float norm = scale / (chosen_sum + 1e-20f);
+    float idw = 0.f;
+    for (int r = 0; r < top; ++r) {
+      const int e = __shfl_sync(0xffffffffu, mine, r);
+      if (e < 0) continue;
+      const float g = s[e] * norm;
+      if (lane == 0) gate[(size_t)t * n_all + e] = g;
+      if (e >= E) idw += g;
+    }
+    if (lane == 0 && identity_weight) identity_weight[t] = idw;
   }
-  if (lane == 0 && identity_weight) identity_weight[t] = idw;
 }
 
-// Refuses: more than 32 chosen experts per token, more than 4096 experts, K above 16384.
-KVB_EXPORT int kvb_route(const void* h, int ld_h, const float* w_router, const float* correction, float* gate,
-                         float* identity_weight, int T_, int K, int E, int n_identity, int top, float scale, int dtype,
-                         cudaStream_t stream) {
+// logits: float32 [T, E + n_identity], the router's products if the caller has made them (h and w_router are not
+// read then), else null.  Refuses: more than 32 chosen experts per token, more than 4096 experts, K above 16384.
+KVB_EXPORT int kvb_route(const void* h, int ld_h, const float* w_router, const float* logits, const float* correction,
+                         float* gate, float* identity_weight, int T_, int K, int E, int n_identity, int top, float scale,
+                         int dtype, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (E < 0 || n_identity < 0 || E + n_identity < 1 || E + n_identity > 4096 || top < 1 || top > 32 || K < 1 || K > 16384)
     return KVB_ERR_BAD_SIZE;
-  const size_t smem = (size_t)kRouteWarps * (K + 2 * (E + n_identity)) * sizeof(float);
+  const int n_all = E + n_identity;
+  // as many tokens a block as their inputs fit 160 KB with, 8 at most; few tokens are spread over more blocks
+  int tb = kRouteTokens;
+  const size_t x_floats = logits ? 0 : (size_t)K;
+  while (tb > 1 && ((size_t)tb * (x_floats + 2 * n_all) * sizeof(float) > 160 * 1024 || (T_ + tb - 1) / tb < 64)) tb >>= 1;
+  const size_t smem = (size_t)tb * (x_floats + 2 * n_all) * sizeof(float);
   if (smem > 200 * 1024) return KVB_ERR_BAD_SIZE;
   KVB_DISPATCH_DTYPE(dtype, T, {
     if (smem > 48 * 1024) {
       cudaError_t err = cudaFuncSetAttribute(route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (err != cudaSuccess) return (int)err;
     }
-    kvb_launch(route_kernel<T>, dim3((T_ + kRouteWarps - 1) / kRouteWarps), dim3(kRouteWarps * 32), smem, stream,
-               (const T*)h, ld_h, w_router, correction, gate, identity_weight, T_, K, E, n_identity, top, scale);
+    kvb_launch(route_kernel<T>, dim3((T_ + tb - 1) / tb), dim3(kRouteWarps * 32), smem, stream, (const T*)h, ld_h, w_router,
+               logits, correction, gate, identity_weight, T_, K, E, n_identity, top, scale, tb);
   });
   return kvb_launch_result();
 }

@@ -827,14 +827,16 @@ __device__ __forceinline__ bool wait_or_abort(void* bar, unsigned parity, volati
 // 64 columns side by side (a row of the 128-byte swizzle holds 64 bfloat16): Q, K and V have DH / 64
 // of them.  The scores take DH / 16 products of 16 along the head, the output DH / 64 times 4
 // products of 64 columns each; tensor memory holds the output in columns 128 .. 128 + DH.
-template <int DH>
+// EXT: kept first keys (their tiles come first in the walk) and the one more in the denominator, see MaskExt; the
+// stride between cached rows is the tensor maps' business.
+template <int DH, bool EXT>
 __global__ void __launch_bounds__(kWsThreads, 2)
 paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                                 int box_rows, const __nv_bfloat16* __restrict__ q_base, int q_row_stride,
                                 const int* __restrict__ block_table, int max_pages, int page_shift, int num_pages,
                                 const int* __restrict__ positions, const TileDesc* __restrict__ tiles,
                                 __nv_bfloat16* __restrict__ out, int nq, int nkv, int G, int gp_shift,
-                                float scale_log2, int window, int* status) {
+                                float scale_log2, int window, int* status, MaskExt ext) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int kSub = DH / 64;                        // sub-tiles of 64 columns in Q, K and V
@@ -892,7 +894,11 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
   const int k_hi = pos_last + 1;
   const int k_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
   const int first_tile = k_lo / BNK, last_tile = (k_hi - 1) / BNK;
-  const int n_tiles = last_tile - first_tile + 1;
+  // the walk: with EXT first the tiles in front of the window's first that hold kept first keys, then the window's
+  const int keep = (EXT && window > 0) ? ext.keep_first : 0;
+  const int keep_tiles = EXT ? min((keep + BNK - 1) / BNK, first_tile) : 0;
+  const int n_tiles = keep_tiles + last_tile - first_tile + 1;
+  auto tile_at = [&](int i) { return i < keep_tiles ? i : first_tile + i - keep_tiles; };
   bool failed = false;
 
   if (warp == 0) {
@@ -908,9 +914,10 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
     // done, a value stage only when the tile's P V is.
     const int total_rows = (num_pages * nkv) << page_shift;
     const int n_box = BNK / box_rows;                 // 1, 2, 4 or 8: a tile never straddles 32 boxes
-    const int first_box = first_tile * n_box;
-    auto pages_of = [&](int chunk) -> int {           // this lane's entry of boxes 32 chunk .. 32 chunk + 31 of the block
-      const int lp = (int)(((long long)(first_box + chunk * 32 + lane) * box_rows) >> page_shift);
+    auto pages_of = [&](int chunk) -> int {           // this lane's entry of boxes 32 chunk .. 32 chunk + 31 of the walk
+      const int vb = chunk * 32 + lane;               // box vb of the walk is box vb % n_box of the walk's tile vb / n_box
+      const int box = tile_at(vb / n_box) * n_box + vb % n_box;
+      const int lp = (int)(((long long)box * box_rows) >> page_shift);
       return lp < max_pages ? __ldg(table + lp) : -1;
     };
     auto request = [&](int i, int pg, unsigned char* dst, const CUtensorMap* map, void* bar) {
@@ -918,11 +925,11 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
       __syncwarp();                                              // the bytes are expected before any copy can report
       const int page = __shfl_sync(0xffffffffu, pg, (i * n_box + lane) & 31);
       if (lane < n_box) {                                        // lane c requests box c of the tile
-        const int kj = (first_tile + i) * BNK + lane * box_rows;
+        const int kj = tile_at(i) * BNK + lane * box_rows;
         int row = total_rows;                                    // zeros
         if (page >= 0 && page < num_pages) {
           row = (((page * nkv) + hk) << page_shift) + (kj & page_mask);
-        } else if (kj < k_hi && kj + box_rows > k_lo) {
+        } else if (kj < k_hi && (kj + box_rows > k_lo || kj < keep)) {
           atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);        // keys that a row reads
         }
 #pragma unroll
@@ -1020,14 +1027,14 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
     float m_ref = -CUDART_INF_F, l_run = 0.f;
     for (int i = 0; i < n_tiles; ++i) {
       const int b = i & 1;
-      const int t = first_tile + i;
+      const int t = tile_at(i);
       if (!wait_or_abort(&bars->s_full[b], (unsigned)(i >> 1) & 1u, abort_flag)) { failed = true; break; }
       tc_fence_after();
       // The row's 64 scores are read once, both halves requested before either is waited for, and
       // stay in registers through the maximum and the probabilities (106 + 32 registers: two blocks
       // per SM still fit).
       const int kb = t * BNK;
-      const bool full = pos >= 0 && kb + BNK - 1 <= pos && kb >= lo;
+      const bool full = pos >= 0 && kb + BNK - 1 <= pos && (kb >= lo || kb + BNK - 1 < keep);
       const bool plain = __all_sync(0xffffffffu, full);
       float v[64];
       tmem_ld32x2(lane_base + 64 * b, v);
@@ -1038,7 +1045,7 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
           const int key = kb + j;
-          if (!(key <= pos && key >= lo)) v[j] = -CUDART_INF_F;
+          if (!(key <= pos && (key >= lo || key < keep))) v[j] = -CUDART_INF_F;
         }
       }
       float m8[8];
@@ -1103,6 +1110,8 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
     }
     if (!failed) {
       tc_fence_after();
+      if (EXT && ext.one_more)       // the one more key: score 0, no value; the sum is in units of 2^m_ref
+        l_run += (m_ref == -CUDART_INF_F) ? 1.f : ex2(-m_ref);
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
       __nv_bfloat16* dst = out + ((size_t)(tile.t0 + ti) * nq + hk * G + hi) * DH;
 #pragma unroll
@@ -1133,38 +1142,38 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
 
 using kvb_page_maps::pages_map;
 
-template <int DH>
+template <int DH, bool EXT = false>
 int launch_ws(const void* q, int q_row_stride, const void* k_pages, const void* v_pages, const int* block_table,
               int max_pages, int page_shift, int num_pages, const int* positions, const void* tiles, int num_tiles,
               void* out, int nq, int nkv, int G, int gp_shift, float scale, int window, int* status,
-              cudaStream_t stream) {
+              cudaStream_t stream, MaskExt ext = MaskExt{DH, 0, 0}) {
   const int page_size = 1 << page_shift;
   const int box_rows = page_size < BNK ? page_size : BNK;
   const long long rows = (long long)num_pages * nkv * page_size;
   if (rows >= (1ll << 31)) return KVB_ERR_BAD_SIZE;
   CUtensorMap mk, mv;
-  int e = pages_map(&mk, k_pages, rows, box_rows, DH);
+  int e = pages_map(&mk, k_pages, rows, box_rows, DH, ext.kv_row_stride);
   if (e) return e;
-  e = pages_map(&mv, v_pages, rows, box_rows, DH);
+  e = pages_map(&mv, v_pages, rows, box_rows, DH, ext.kv_row_stride);
   if (e) return e;
   constexpr int kKSt = DH == 64 ? 3 : 2, kVSt = DH == 64 ? 3 : 1, kPB = DH == 64 ? 2 : 1;   // as in the kernel
   const size_t smem = 1024 + (size_t)BM * DH * 2 + (kKSt + kVSt) * (size_t)BNK * DH * 2 + kPB * kPBytes + sizeof(WsBars) + 64;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t ce = cudaFuncSetAttribute(paged_flash_attention_ws_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t ce = cudaFuncSetAttribute(paged_flash_attention_ws_kernel<DH, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem);
     if (ce != cudaSuccess) return (int)ce;
     // two blocks per SM need the largest shared-memory configuration
-    ce = cudaFuncSetAttribute(paged_flash_attention_ws_kernel<DH>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    ce = cudaFuncSetAttribute(paged_flash_attention_ws_kernel<DH, EXT>, cudaFuncAttributePreferredSharedMemoryCarveout,
                               (int)cudaSharedmemCarveoutMaxShared);
     if (ce != cudaSuccess) return (int)ce;
     attr_set = true;
   }
   dim3 grid(num_tiles, nkv);
-  kvb_launch(paged_flash_attention_ws_kernel<DH>, grid, dim3(kWsThreads), smem, stream, mk, mv, box_rows,
+  kvb_launch(paged_flash_attention_ws_kernel<DH, EXT>, grid, dim3(kWsThreads), smem, stream, mk, mv, box_rows,
              (const __nv_bfloat16*)q, q_row_stride, block_table, max_pages, page_shift,
              num_pages, positions, (const TileDesc*)tiles, (__nv_bfloat16*)out, nq, nkv, G, gp_shift,
-             scale * 1.4426950408889634f, window, status);
+             scale * 1.4426950408889634f, window, status, ext);
   return kvb_launch_result();
 }
 
@@ -1260,7 +1269,8 @@ KVB_EXPORT int kvb_paged_flash_attention(const void* q, int q_row_stride, const 
 // The mma.sync form above for mixers whose mask and softmax go beyond the plain causal window (see MaskExt):
 // key and value of a token lie side by side in one pool, `pages` [num_pages, nkv, page_size, 2 d]; query i sees
 // key j when j <= i and (i - j < window or j < keep_first) (window 0: every key up to i); with one_more the
-// softmax's denominator is 1 + sum exp(s).  Key and value size are both d (64 or 128).  wide: 0 or 1 as above.
+// softmax's denominator is 1 + sum exp(s).  Key and value size are both d (64 or 128).  wide: 0 or 1 as above (mma.sync),
+// or 3: the tcgen05 form with roles on 128-row tiles (pages of at least 8 rows), built with the same additions.
 KVB_EXPORT int kvb_paged_flash_attention_rows(const void* q, int q_row_stride, const void* pages, const int* block_table,
                                               int max_pages, int page_size, int num_pages, const int* positions,
                                               const void* tiles, int num_tiles, int wide, void* out, int nq, int nkv,
@@ -1278,6 +1288,14 @@ KVB_EXPORT int kvb_paged_flash_attention_rows(const void* q, int q_row_stride, c
   if (wide && (128 >> gp_shift) < 1) return KVB_ERR_BAD_SIZE;
   const MaskExt ext{2 * d, keep_first, one_more};
   const void* values = static_cast<const __nv_bfloat16*>(pages) + d;
+  if (wide == 3) {   // the tcgen05 form with roles: 128-row tiles, pages of at least 8 rows
+    if (page_size < 8) return KVB_ERR_BAD_SIZE;
+    if (d == 64)
+      return tc5::launch_ws<64, true>(q, q_row_stride, pages, values, block_table, max_pages, page_shift, num_pages,
+                                      positions, tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, window, status, stream, ext);
+    return tc5::launch_ws<128, true>(q, q_row_stride, pages, values, block_table, max_pages, page_shift, num_pages,
+                                     positions, tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, window, status, stream, ext);
+  }
 #define KVB_FA_EXT(D, NW)                                                                                              \
   return (launch<D, NW, true>(q, q_row_stride, pages, values, block_table, max_pages, page_shift, num_pages, positions, \
                               tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, window, status, stream, ext))

@@ -16,8 +16,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 struct MapKey {
-  const void* ptr; long long rows; int box, dh;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && box == o.box && dh == o.dh; }
+  const void* ptr; long long rows; int box, dh, pitch;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && box == o.box && dh == o.dh && pitch == o.pitch;
+  }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const { return std::hash<const void*>()(k.ptr) ^ (size_t)k.rows * 2654435761u ^ (size_t)k.box; }
@@ -27,8 +29,9 @@ inline std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 
 // The pages of one layer, [num_pages x nkv x page_size rows][head size] bfloat16, as a 2-D tensor
 // map with boxes of box_rows x 64 and the 128-byte swizzle.  Rows beyond the last one read as zeros.
+// pitch: elements from one row to the next (0: dh; more when a row of the pool holds other columns beside these).
 // Encoded once per address and shape.  ptr must be 16-byte aligned.
-inline int pages_map(CUtensorMap* out, const void* ptr, long long rows, int box_rows, int dh) {
+inline int pages_map(CUtensorMap* out, const void* ptr, long long rows, int box_rows, int dh, int pitch = 0) {
   static EncodeTiledFn fn = nullptr;
   std::lock_guard<std::mutex> lock(g_map_mutex);
   if (!fn) {
@@ -39,12 +42,13 @@ inline int pages_map(CUtensorMap* out, const void* ptr, long long rows, int box_
       return KVB_ERR_BAD_SIZE;
     fn = reinterpret_cast<EncodeTiledFn>(p);
   }
-  MapKey key{ptr, rows, box_rows, dh};
+  if (pitch <= 0) pitch = dh;
+  MapKey key{ptr, rows, box_rows, dh, pitch};
   auto it = g_maps.find(key);
   if (it == g_maps.end()) {
     CUtensorMap m;
     cuuint64_t dims[2] = {(cuuint64_t)dh, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)dh * 2};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
     cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
     CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,

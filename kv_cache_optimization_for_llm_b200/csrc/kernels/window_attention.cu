@@ -195,6 +195,231 @@ window_attention_kernel(const T* __restrict__ q_base, int q_row_stride, const T*
   }
 }
 
+// The same attention with the query heads that share a key/value head in one block: a cached row is read
+// once for all of them.  One block per (query token, key/value head); chunk c of 32 keys goes to warp
+// c % kGroupWarps as above; a lane scores its key against every head of the group, and in the weighted sum
+// owns VPL consecutive value channels (one vector load per key).  Takes groups of up to 8 heads and values
+// of up to 128 channels that are a multiple of 32 wide; the launcher falls back to the kernel above otherwise.
+constexpr int kGroupWarps = 8;
+constexpr int kMaxGroup = 8;
+
+template <typename T, int VPL>
+__device__ __forceinline__ void load_values(const T* v, float* x);
+template <> __device__ __forceinline__ void load_values<float, 1>(const float* v, float* x) { x[0] = v[0]; }
+template <> __device__ __forceinline__ void load_values<float, 2>(const float* v, float* x) {
+  const float2 a = *reinterpret_cast<const float2*>(v); x[0] = a.x; x[1] = a.y;
+}
+template <> __device__ __forceinline__ void load_values<float, 4>(const float* v, float* x) {
+  const float4 a = *reinterpret_cast<const float4*>(v); x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+}
+template <> __device__ __forceinline__ void load_values<__nv_bfloat16, 1>(const __nv_bfloat16* v, float* x) {
+  x[0] = __bfloat162float(v[0]);
+}
+template <> __device__ __forceinline__ void load_values<__nv_bfloat16, 2>(const __nv_bfloat16* v, float* x) {
+  const unsigned a = *reinterpret_cast<const unsigned*>(v);
+  x[0] = __uint_as_float(a << 16); x[1] = __uint_as_float(a & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void load_values<__nv_bfloat16, 4>(const __nv_bfloat16* v, float* x) {
+  const uint2 a = *reinterpret_cast<const uint2*>(v);
+  x[0] = __uint_as_float(a.x << 16); x[1] = __uint_as_float(a.x & 0xffff0000u);
+  x[2] = __uint_as_float(a.y << 16); x[3] = __uint_as_float(a.y & 0xffff0000u);
+}
+
+__device__ __forceinline__ void load_16_bytes(const float* p, float* x) {
+  const float4 u = *reinterpret_cast<const float4*>(p);
+  x[0] = u.x; x[1] = u.y; x[2] = u.z; x[3] = u.w;
+}
+__device__ __forceinline__ void load_16_bytes(const __nv_bfloat16* p, float* x) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { x[2 * e] = __uint_as_float(w[e] << 16); x[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u); }
+}
+
+template <typename T, int VPL, int GP>
+__global__ void __launch_bounds__(kGroupWarps * 32)
+window_attention_group_kernel(const T* __restrict__ q_base, int q_row_stride, const T* __restrict__ pages,
+                              const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
+                              const int* __restrict__ positions, const int* __restrict__ token_req, T* __restrict__ out,
+                              int nq, int nkv, int Dk, float scale, int window, int keep_first, int one_more, int vec,
+                              int* status) {
+  constexpr int Dv = VPL * 32;
+  extern __shared__ float gsm[];
+  float* q_s = gsm;                                  // [GP][Dk]
+  float* acc_s = q_s + GP * Dk;                      // [kGroupWarps][GP][Dv]
+  float* m_s = acc_s + kGroupWarps * GP * Dv;        // [kGroupWarps][GP]
+  float* l_s = m_s + kGroupWarps * GP;               // [kGroupWarps][GP]
+
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, hk = blockIdx.y;
+  const int G = nq / nkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos = positions[t];
+  const int* table = block_table + (size_t)token_req[t] * max_pages;
+  const int row_len = Dk + Dv;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int keep = window > 0 ? keep_first : 0;
+  const int keep_chunks = (keep + 31) / 32;
+  const int lo_chunk = lo / 32;
+
+  const T* q = q_base + (size_t)t * q_row_stride + (size_t)hk * G * Dk;
+  for (int i = threadIdx.x; i < GP * Dk; i += blockDim.x) q_s[i] = (i < G * Dk) ? to_f32(q[i]) : 0.f;
+  __syncthreads();
+
+  float m[GP], l[GP], acc[GP][VPL];
+#pragma unroll
+  for (int g = 0; g < GP; ++g) {
+    m[g] = -CUDART_INF_F; l[g] = 0.f;
+#pragma unroll
+    for (int r = 0; r < VPL; ++r) acc[g][r] = 0.f;
+  }
+
+  for (int c = warp; c * 32 <= pos; c += kGroupWarps) {
+    if (c >= keep_chunks && c < lo_chunk) {
+      c += (lo_chunk - c + kGroupWarps - 1) / kGroupWarps * kGroupWarps - kGroupWarps;
+      continue;
+    }
+    const int j = c * 32 + lane;
+    const bool valid = j <= pos && (j >= lo || j < keep);
+    long long off = -1;
+    float s[GP];
+#pragma unroll
+    for (int g = 0; g < GP; ++g) s[g] = -CUDART_INF_F;
+    if (valid) {
+      const int lp = j / page_size;
+      const int page = lp < max_pages ? table[lp] : -1;
+      if (page < 0 || page >= num_pages) {
+        atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+      } else {
+        off = (((long long)page * nkv + hk) * page_size + (j % page_size)) * row_len;
+        const T* k = pages + off;
+        float dot[GP];
+#pragma unroll
+        for (int g = 0; g < GP; ++g) dot[g] = 0.f;
+        if (vec) {
+          constexpr int PER = 16 / (int)sizeof(T);
+#pragma unroll 4
+          for (int i = 0; i < Dk; i += PER) {     // unrolled: the row's loads are all requested before the first is used
+            float x[PER];
+            load_16_bytes(k + i, x);
+#pragma unroll
+            for (int e4 = 0; e4 < PER; e4 += 4) {
+#pragma unroll
+              for (int g = 0; g < GP; ++g) {
+                const float4 qv = *reinterpret_cast<const float4*>(q_s + g * Dk + i + e4);
+                dot[g] = fmaf(qv.x, x[e4], dot[g]); dot[g] = fmaf(qv.y, x[e4 + 1], dot[g]);
+                dot[g] = fmaf(qv.z, x[e4 + 2], dot[g]); dot[g] = fmaf(qv.w, x[e4 + 3], dot[g]);
+              }
+            }
+          }
+        } else {
+          for (int i = 0; i < Dk; ++i) {
+            const float x = to_f32(k[i]);
+#pragma unroll
+            for (int g = 0; g < GP; ++g) dot[g] = fmaf(q_s[g * Dk + i], x, dot[g]);
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < GP; ++g) s[g] = dot[g] * scale;
+      }
+    }
+    if (warp_max(off >= 0 ? 1.f : -CUDART_INF_F) == -CUDART_INF_F) continue;   // nothing readable in this chunk
+    float p[GP];
+#pragma unroll
+    for (int g = 0; g < GP; ++g) {
+      const float m_new = fmaxf(m[g], warp_max(s[g]));
+      const float corr = (m[g] == -CUDART_INF_F) ? 0.f : expf(m[g] - m_new);
+      p[g] = (off >= 0) ? expf(s[g] - m_new) : 0.f;
+      l[g] = l[g] * corr + warp_sum(p[g]);
+#pragma unroll
+      for (int r = 0; r < VPL; ++r) acc[g][r] *= corr;
+      m[g] = m_new;
+    }
+    // the values of eight keys are requested together: one key's load after the other would cost a trip to memory each
+    const int n_in_chunk = min(32, pos - c * 32 + 1);
+    for (int jj0 = 0; jj0 < n_in_chunk; jj0 += 8) {
+      float x[8][VPL];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const long long oj = __shfl_sync(0xffffffffu, off, (jj0 + u) & 31);
+        if (oj >= 0 && jj0 + u < n_in_chunk) {
+          load_values<T, VPL>(pages + oj + Dk + lane * VPL, x[u]);
+        } else {
+#pragma unroll
+          for (int r = 0; r < VPL; ++r) x[u][r] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+#pragma unroll
+        for (int g = 0; g < GP; ++g) {
+          const float pj = __shfl_sync(0xffffffffu, p[g], (jj0 + u) & 31);     // 0 for a key that is not seen
+#pragma unroll
+          for (int r = 0; r < VPL; ++r) acc[g][r] = fmaf(pj, x[u][r], acc[g][r]);
+        }
+      }
+    }
+  }
+
+#pragma unroll
+  for (int g = 0; g < GP; ++g) {
+    if (lane == 0) { m_s[warp * GP + g] = m[g]; l_s[warp * GP + g] = l[g]; }
+#pragma unroll
+    for (int r = 0; r < VPL; ++r) acc_s[(warp * GP + g) * Dv + lane * VPL + r] = acc[g][r];
+  }
+  __syncthreads();
+  // warp g finishes head g: the warps' partial sums are merged in the order of the warps
+  for (int g = warp; g < G; g += kGroupWarps) {
+    float M = one_more ? 0.f : -CUDART_INF_F;       // the one more key's score is 0
+    for (int w = 0; w < kGroupWarps; ++w) M = fmaxf(M, m_s[w * GP + g]);
+    float L = one_more ? expf(-M) : 0.f, f[kGroupWarps];
+    for (int w = 0; w < kGroupWarps; ++w) {
+      const float mw = m_s[w * GP + g];
+      f[w] = (mw == -CUDART_INF_F) ? 0.f : expf(mw - M);
+      L += l_s[w * GP + g] * f[w];
+    }
+    T* o = out + ((size_t)t * nq + hk * G + g) * Dv;
+    for (int i = lane; i < Dv; i += 32) {
+      float a = 0.f;
+      for (int w = 0; w < kGroupWarps; ++w) a += acc_s[(w * GP + g) * Dv + i] * f[w];
+      o[i] = from_f32<T>(L > 0.f ? a / L : 0.f);
+    }
+  }
+}
+
+template <typename T, int VPL, int GP>
+static int launch_group(const void* q, int q_row_stride, const void* pages, const int* block_table, int max_pages,
+                        int page_size, int num_pages, const int* positions, const int* token_req, void* out, int T_,
+                        int nq, int nkv, int Dk, float scale, int window, int keep_first, int one_more, int vec,
+                        int* status, cudaStream_t stream) {
+  const size_t smem = ((size_t)GP * Dk + (size_t)kGroupWarps * GP * (VPL * 32 + 2)) * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(window_attention_group_kernel<T, VPL, GP>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  kvb_launch(window_attention_group_kernel<T, VPL, GP>, dim3(T_, nkv), dim3(kGroupWarps * 32), smem, stream, (const T*)q,
+             q_row_stride, (const T*)pages, block_table, max_pages, page_size, num_pages, positions, token_req, (T*)out, nq,
+             nkv, Dk, scale, window, keep_first, one_more, vec, status);
+  return kvb_launch_result();
+}
+
+template <typename T, int VPL>
+static int launch_group_gp(int G, const void* q, int q_row_stride, const void* pages, const int* block_table,
+                           int max_pages, int page_size, int num_pages, const int* positions, const int* token_req,
+                           void* out, int T_, int nq, int nkv, int Dk, float scale, int window, int keep_first,
+                           int one_more, int vec, int* status, cudaStream_t stream) {
+#define KVB_WG(GP) return launch_group<T, VPL, GP>(q, q_row_stride, pages, block_table, max_pages, page_size, num_pages, \
+                                                   positions, token_req, out, T_, nq, nkv, Dk, scale, window, keep_first, \
+                                                   one_more, vec, status, stream)
+  if (G == 1) KVB_WG(1);
+  if (G == 2) KVB_WG(2);
+  if (G <= 4) KVB_WG(4);
+  KVB_WG(8);
+#undef KVB_WG
+}
+
 // q points at the first query head of token 0; consecutive tokens are q_row_stride elements apart.
 // pages: [num_pages, nkv, page_size, Dk + Dv].  out is [T, nq * Dv], dense.
 // Refuses: Dk or Dv above 256, nq not a multiple of nkv, a negative window or keep_first.
@@ -209,6 +434,19 @@ KVB_EXPORT int kvb_window_attention(const void* q, int q_row_stride, const void*
   const int esz = dtype == KVB_F32 ? 4 : 2;
   const int per16 = 16 / esz;
   const int vec = (Dk % per16 == 0 && (Dk + Dv) % per16 == 0 && ((uintptr_t)pages % 16) == 0) ? 1 : 0;
+  // groups of up to 8 heads with values of 32, 64 or 128 channels: a block per key/value head, the rows read once
+  const int G = nq / nkv;
+  if (G <= kMaxGroup && (Dv == 32 || Dv == 64 || Dv == 128) && vec) {
+#define KVB_WV(VPL)                                                                                                     \
+  KVB_DISPATCH_DTYPE(dtype, T, return (launch_group_gp<T, VPL>(G, q, q_row_stride, pages, block_table, max_pages,      \
+                                                               page_size, num_pages, positions, token_req, out, T_, nq, \
+                                                               nkv, Dk, scale, window, keep_first, one_more, vec,      \
+                                                               status, stream)))
+    if (Dv == 32) { KVB_WV(1); }
+    if (Dv == 64) { KVB_WV(2); }
+    if (Dv == 128) { KVB_WV(4); }
+#undef KVB_WV
+  }
   dim3 grid(T_, nq);
   KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(window_attention_kernel<T>, grid, dim3(kWarps * 32), 0, stream, (const T*)q,
                                             q_row_stride, (const T*)pages, block_table, max_pages, page_size, num_pages,

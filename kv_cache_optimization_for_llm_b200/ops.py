@@ -462,22 +462,46 @@ def delta_scan(mode: str, batch, state: torch.Tensor, r, k, v, gate, decay, aux,
     return out
 
 
+class _AppendArgs(ctypes.Structure):
+    _fields_ = [("pages", c_void_p), ("block_table", c_void_p), ("max_pages", c_int), ("page_size", c_int),
+                ("num_pages", c_int), ("k_off", c_int), ("v_off", c_int), ("kv_heads", c_int), ("Dk", c_int), ("Dv", c_int),
+                ("status", c_void_p)]
+
+
+def conv_can_append(x: torch.Tensor, first: int, channels: int, k_off: int, v_off: int, dk: int, dv: int) -> bool:
+    """Whether :func:`conv_silu` can write keys and values into their pages itself: every run of channels starts and
+    ends on a 16-byte boundary."""
+    vec = 16 // x.element_size()
+    return (channels % vec == 0 and x.stride(0) % vec == 0 and _at(x, first) % 16 == 0 and dk % vec == 0 and dv % vec == 0
+            and k_off % vec == 0 and v_off % vec == 0)
+
+
 def conv_silu(x: torch.Tensor, first: int, channels: int, w: torch.Tensor, tails: Optional[torch.Tensor],
-              batch, act: str = "silu") -> torch.Tensor:
+              batch, act: str = "silu", append=None) -> torch.Tensor:
     """``silu`` (``act`` "none": nothing) of a short causal convolution over time per channel of ``x[:, first:first + channels]``.
     ``w`` float32 [channels, taps], last column for the token itself.  ``tails``: float32
     [slots, >= (taps - 1) * channels], a view whose row r starts with request slot r's last
-    ``taps - 1`` inputs; it is read for the inputs in front of the step's tokens and brought up to date."""
+    ``taps - 1`` inputs; it is read for the inputs in front of the step's tokens and brought up to date.
+    ``append``: (pages, block_table, k_off, v_off, kv_heads, dk, dv): the results from channel ``k_off`` on are
+    ``kv_heads`` keys of ``dk``, those from ``v_off`` on values of ``dv``, and they are also written into the requests'
+    pages [num_pages, kv_heads, page_size, dk + dv] (only when :func:`conv_can_append` says so)."""
     _need_cuda(x, w)
     taps = w.shape[1]
     assert w.dtype == torch.float32 and w.is_contiguous() and x.stride(1) == 1
     assert taps == 1 or (tails is not None and tails.dtype == torch.float32 and tails.stride(-1) == 1)
     out = new((x.shape[0], channels), x.dtype, x.device)
+    ap = None
+    if append is not None:
+        pages, table, k_off, v_off, kv_heads, dk, dv = append
+        assert pages.is_contiguous() and pages.dtype == x.dtype and tuple(pages.shape[1:]) == (kv_heads, pages.shape[2], dk + dv)
+        ap = _AppendArgs(pages.data_ptr(), table.data_ptr(), table.shape[1], pages.shape[2], pages.shape[0], k_off, v_off,
+                         kv_heads, dk, dv, batch.status.data_ptr())
     rc = lib("delta_rule").kvb_conv_silu(
         c_void_p(_at(x, first)), c_int(x.stride(0)), _p(w), c_int(taps), _p(tails),
         c_longlong(0 if tails is None else tails.stride(0)), _p(out), c_int(channels), c_int(x.shape[0]),
         c_int(batch.num_reqs), _p(batch.positions), _p(batch.token_req), _p(batch.q_start), _p(batch.req_start),
-        _p(batch.ctx_len), _p(batch.slots), c_int({"silu": 0, "none": 1}[act]), c_int(dtype_code(x.dtype)), _stream())
+        _p(batch.ctx_len), _p(batch.slots), c_int({"silu": 0, "none": 1}[act]),
+        ctypes.byref(ap) if ap is not None else None, c_int(dtype_code(x.dtype)), _stream())
     _check(rc, "conv_silu")
     global launch_count
     launch_count += 1 if taps > 1 else 0   # the convolution and the tails' update
@@ -675,47 +699,66 @@ def flash_attention_rows_supported(dk: int, dv: int, group: int, page_size: int,
     return dtype == torch.bfloat16 and dk == dv and flash_attention_supported(dk, group, page_size)
 
 
+# Which form the tensor-core attention over [key | value] rows takes: None: chosen from the step's size as for the
+# rotary attention (128-row tiles on tcgen05 when they fill the GPU, else 64-row tiles on mma.sync); 0, 1 or 3 forces
+# 64-row tiles, 128-row tiles on mma.sync, or the tcgen05 form with roles.
+FLASH_ROWS_WIDE = {"": None, "0": 0, "1": 1, "3": 3}[os.environ.get('KVB200_FLASH_ROWS_WIDE', '')]
+
+
 def flash_attention_rows(q: torch.Tensor, pages: torch.Tensor, block_table, batch, heads: int, kv_heads: int, d: int,
                          scale: float, window: int, keep_first: int, one_more: bool,
-                         wide: Optional[bool] = None) -> torch.Tensor:
+                         wide: Optional[int] = None) -> torch.Tensor:
     """:func:`window_attention` on tensor cores for steps with runs of query tokens (bfloat16, key and value
     size ``d`` both): tiles of 64 or 128 (token, head of a group) rows against tiles of 64 keys, the tiles that
-    hold kept first keys in front of the window's own.  Queries at ``q[:, : heads * d]``."""
+    hold kept first keys in front of the window's own.  Queries at ``q[:, : heads * d]``.  ``wide``: 0: 64-row tiles
+    (mma.sync); 1: 128-row tiles (mma.sync); 3: 128-row tiles on tcgen05 with roles (pages of at least 8 rows);
+    None: chosen from the step's size."""
     _need_cuda(q, pages)
     assert q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and pages.is_contiguous() and q.stride(1) == 1
     assert tuple(pages.shape[1:]) == (kv_heads, pages.shape[2], 2 * d)
     T = q.shape[0]
     group = heads // kv_heads
     if wide is None:
+        wide = FLASH_ROWS_WIDE
+    if wide is None:
         wide = FLASH_WIDE and (T // flash_tokens_per_tile(group, True)) * kv_heads >= (2 if d == 64 else 1) * sm_count(q.device)
+        if wide and FLASH_TC and FLASH_TC_ROLES:
+            wide = 3
+    wide = int(wide)
+    if wide == 3 and not (pages.shape[2] >= 8 and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0):
+        wide = 1
     tiles = flash_tiles(batch, group, bool(wide))
     out = new((T, heads * d), q.dtype, q.device)
     rc = lib("flash_attention").kvb_paged_flash_attention_rows(
         _p(q), c_int(q.stride(0)), _p(pages), _p(block_table), c_int(block_table.shape[1]), c_int(pages.shape[2]),
-        c_int(pages.shape[0]), _p(batch.positions), _p(tiles), c_int(tiles.shape[0]), c_int(1 if wide else 0), _p(out),
+        c_int(pages.shape[0]), _p(batch.positions), _p(tiles), c_int(tiles.shape[0]), c_int(wide), _p(out),
         c_int(heads), c_int(kv_heads), c_int(d), c_float(scale), c_int(int(window or 0)), c_int(int(keep_first or 0)),
         c_int(1 if one_more else 0), _p(batch.status), _stream())
     _check(rc, "flash_attention_rows")
     choices["flash_attention_rows"] += 1
+    choices[f"flash_attention_rows_{wide}"] += 1
     return out
 
 
 # ------------------------------------------------------------------ routed experts
 
 def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, experts: int, identity: int, top: int,
-          scale: float):
+          scale: float, logits: Optional[torch.Tensor] = None):
     """The router of a feed-forward of many experts.  ``w_router`` float32 [experts + identity, K],
     ``correction`` float32 [experts + identity] (added to the scores for the choice only).  Returns
     ``gate`` float32 [T, experts + identity], a token's weight for every expert (0 where not chosen), and
-    float32 [T], the summed weights of its identity experts (None without any)."""
+    float32 [T], the summed weights of its identity experts (None without any).  ``logits``: float32
+    [T, experts + identity], the products ``h . w_router^T`` if the caller has made them already (by a matrix
+    product that adds up in float32), in which case the kernel only chooses."""
     _need_cuda(h, w_router)
     T, K = h.shape
     n_all = experts + identity
     assert w_router.dtype == torch.float32 and w_router.is_contiguous() and tuple(w_router.shape) == (n_all, K)
     assert correction.dtype == torch.float32 and correction.numel() == n_all and h.stride(1) == 1
+    assert logits is None or (logits.dtype == torch.float32 and logits.is_contiguous() and tuple(logits.shape) == (T, n_all))
     gate = new((T, n_all), torch.float32, h.device)
     idw = new((T,), torch.float32, h.device) if identity else None
-    rc = lib("experts").kvb_route(_p(h), c_int(h.stride(0)), _p(w_router), _p(correction), _p(gate), _p(idw), c_int(T),
+    rc = lib("experts").kvb_route(_p(h), c_int(h.stride(0)), _p(w_router), _p(logits), _p(correction), _p(gate), _p(idw), c_int(T),
                                   c_int(K), c_int(experts), c_int(identity), c_int(top), c_float(scale),
                                   c_int(dtype_code(h.dtype)), _stream())
     _check(rc, "route")

@@ -66,13 +66,23 @@ class RoutedExperts(Part):
         else:
             self.up = self.down = None
         self.router, self.correction = weights["router"], weights["correction"]
+        # The router's products are float32 sums of float32 products.  Where the compute type holds the router's
+        # weights exactly (a checkpoint stored in that type), the step's matrix product kernels make them (tensor
+        # cores add up bfloat16 products exactly in float32); otherwise the routing kernel does, on float32 weights.
+        self.router_in_compute_type = None
+        lowp = self.router.to(ctx.dtype)
+        if self.hidden % 8 == 0 and torch.equal(lowp.float(), self.router):
+            self.router_in_compute_type = lowp.contiguous()
 
     def activation_widths(self):
         w = self.width + self.pad
-        return [2 * (self.E + self.I) + 2, w, w, self.hidden]
+        return [4 * (self.E + self.I) + 2, w, w, self.hidden]
 
     def forward(self, x, batch):
-        gate, identity_weight = ops.route(x, self.router, self.correction, self.E, self.I, self.top, self.scale)
+        logits = None
+        if self.router_in_compute_type is not None:
+            logits = ops.linear(x, self.router_in_compute_type, out_dtype=torch.float32)
+        gate, identity_weight = ops.route(x, self.router, self.correction, self.E, self.I, self.top, self.scale, logits)
         if self.up is not None:
             a = ops.expert_act(ops.linear(x, self.up), gate, self.E, self.F, self.S + self.pad)
             y = ops.linear(a, self.down)

@@ -87,9 +87,12 @@ class ConvWindowAttention(Part):
 
     def forward(self, x, batch, cache):
         p = ops.linear(x, self.qkv)
-        c = ops.conv_silu(p, 0, self.channels, self.conv_w, cache.state, batch, act="none")
         table = batch.block_tables[cache.group]
-        if cache.write:
+        # the convolution writes the new keys and values into their pages itself where the rows allow 16-byte accesses
+        fused = cache.write and ops.conv_can_append(p, 0, self.channels, self.k_off, self.v_off, self.dim, self.vdim)
+        c = ops.conv_silu(p, 0, self.channels, self.conv_w, cache.state, batch, act="none",
+                          append=(cache.k, table, self.k_off, self.v_off, self.kv_heads, self.dim, self.vdim) if fused else None)
+        if cache.write and not fused:
             ops.kv_rows_append(c, self.k_off, self.v_off, cache.k, table, batch, self.kv_heads, self.dim, self.vdim)
         if not batch.decode_only and self._on_tensor_cores(cache.page_size) and c.stride(0) % 8 == 0:
             a = ops.flash_attention_rows(c, cache.k, table, batch, self.heads, self.kv_heads, self.dim, self.scale,

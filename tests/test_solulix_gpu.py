@@ -206,7 +206,7 @@ def test_attention_alone_in_portions_and_beside_another_request(dtype, shape):
     assert _same(one[0], whole[1], dtype), "token by token"
 
 
-def _spiked(dtype, size, keep_first, T, query, key, page=8, D=16):
+def _spiked(dtype, size, keep_first, T, query, key, page=8, D=16, wide=None):
     """The attention kernels alone on keys and values made so that one key decides: every query and key
     is small but the pair (query, key), whose score is 30; the value of key j is the unit vector j (``D`` 16) or,
     with key and value size ``D`` both (the sizes the tensor-core kernel takes), the unit vector j mod D.
@@ -241,7 +241,8 @@ def _spiked(dtype, size, keep_first, T, query, key, page=8, D=16):
             part = src[at:at + n].contiguous()
             ops.kv_rows_append(part, D, 2 * D, pages, batch.block_tables[0], batch, 1, D, Dv)
             if n > 1 and ops.flash_attention_rows_supported(D, Dv, 1, page, DT[dtype]):
-                got = ops.flash_attention_rows(part, pages, batch.block_tables[0], batch, 1, 1, D, 1.0, size, keep_first, True)
+                got = ops.flash_attention_rows(part, pages, batch.block_tables[0], batch, 1, 1, D, 1.0, size, keep_first, True,
+                                               wide=wide)
             else:
                 got = ops.window_attention(part, 0, pages, batch.block_tables[0], batch, 1, 1, D, Dv, 1.0, size, keep_first, True)
             rows.append(got.float().cpu())
@@ -277,15 +278,17 @@ def test_a_key_far_away_and_keys_at_the_edges_of_the_window_and_of_the_kept_toke
     assert abs(in_prompt[0] - ref[0]) < 1e-2 and 0.4 < ref[0] < 0.6
 
 
+@pytest.mark.parametrize("wide", [0, 1, 3])
 @pytest.mark.parametrize("D", [64, 128])
-def test_the_same_edges_on_the_tensor_core_kernel_of_prompt_portions(D):
-    """bfloat16 with key and value size 64 or 128: kept first tokens that fill more than one tile of 64 keys in
-    front of a window that starts tiles later, keys on both sides of every edge, and of a tile's border."""
+def test_the_same_edges_on_the_tensor_core_kernels_of_prompt_portions(D, wide):
+    """bfloat16 with key and value size 64 or 128, on 64-row and 128-row tiles (mma.sync) and on the tcgen05 form with
+    roles: kept first tokens that fill more than one tile of 64 keys in front of a window that starts tiles later,
+    keys on both sides of every edge, and of a tile's border."""
     size, keep = 37, 70
     T, query = 400, 390
     for key, seen in ((query - size + 1, True), (query - size, False), (keep - 1, True), (keep, False), (0, True), (63, True),
                       (64, True), (query, True), (query - 6, True), (200, False), (128, False), (127, False)):
-        (in_prompt, decoded), ref = _spiked("bfloat16", size, keep, T, query, key, D=D)
+        (in_prompt, decoded), ref = _spiked("bfloat16", size, keep, T, query, key, D=D, wide=wide)
         for got in (in_prompt, decoded):
             if seen:
                 assert got[key % D] > 0.97, (key, got[key % D])
@@ -294,17 +297,19 @@ def test_the_same_edges_on_the_tensor_core_kernel_of_prompt_portions(D):
             assert np.abs(got - ref).max() < 1e-2
     # kept first tokens that the window still covers (no tile in front of the window's own), and no window at all
     for size, keep, key, seen in ((300, 20, 95, True), (300, 20, 90, False), (0, 0, 1, True)):
-        (in_prompt, decoded), ref = _spiked("bfloat16", size, keep, T, query, key, D=D)
+        (in_prompt, decoded), ref = _spiked("bfloat16", size, keep, T, query, key, D=D, wide=wide)
         assert (in_prompt[key % D] > 0.97) == seen and np.abs(in_prompt - ref).max() < 1e-2
 
 
 @pytest.mark.parametrize("shape", [dict(heads=4, kv_heads=2, dim=64, vdim=64, conv=3, size=50, keep_first=70),
                                    dict(heads=3, kv_heads=1, dim=128, vdim=128, conv=2, size=100, keep_first=5),
                                    dict(heads=2, kv_heads=2, dim=64, vdim=64, conv=4, size=1000, keep_first=0)])
-def test_attention_on_tensor_cores_in_long_portions(shape):
+@pytest.mark.parametrize("wide", [None, 3])
+def test_attention_on_tensor_cores_in_long_portions(shape, wide, monkeypatch):
     """The mixer in bfloat16 at sizes whose prompt portions run on tensor cores: 300 and 130 tokens, whole, and
     cut into portions beside single tokens of the other request."""
     from kv_cache_optimization_for_llm_b200 import ops
+    monkeypatch.setattr(ops, "FLASH_ROWS_WIDE", wide)
     rng = np.random.default_rng(11)
     dtype = "bfloat16"
     ctx = _ctx(dtype)
@@ -321,6 +326,8 @@ def test_attention_on_tensor_cores_in_long_portions(shape):
     cut = _run_in_steps(mixer, ctx, xs, [[(0, 129), (1, 1)], [(0, 2), (1, 1)], [(0, 65), (1, 100)], [(0, 1), (1, 1)],
                                          [(0, 100), (1, 27)], [(0, 1)], [(0, 1)], [(0, 1)]])
     assert ops.choices["flash_attention_rows"] >= before + 6
+    if wide == 3:
+        assert ops.choices["flash_attention_rows_3"] >= 6
     for r in xs:
         assert _err(whole[r], refs[r], dtype) < TOL[dtype]
         assert _err(cut[r], refs[r], dtype) < TOL[dtype]
