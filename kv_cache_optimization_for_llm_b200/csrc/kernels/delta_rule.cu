@@ -441,8 +441,21 @@ __global__ void conv_vec_kernel(const T* __restrict__ in, int ld, const float* _
   if (idx >= (long long)T_ * groups) return;
   const int t = (int)(idx / groups), c = (int)(idx - (long long)t * groups) * VEC;
   const int pos = positions[t], r = token_req[t];
-  const int start = req_start[r], row0 = q_start[r];
-  const float* tail = tails + (size_t)slots[r] * slot_stride;
+  // A request's tokens of this step are consecutive rows: the input `back` tokens back is row t - back when that row
+  // belongs to the same request, which one look at token_req tells; only the first taps - 1 tokens of a run go on to
+  // the request's tail (and look up where it lies).
+  auto older = [&](int back, float* x) {
+    const int sp = pos - back;
+    if (sp < 0) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) x[e] = 0.f;
+      return;
+    }
+    const int start = req_start[r];
+    const float* tp = tails + (size_t)slots[r] * slot_stride + (size_t)(sp - (start - (taps - 1))) * C + c;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) x[e] = tp[e];
+  };
   float acc[VEC];
 #pragma unroll
   for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
@@ -454,35 +467,27 @@ __global__ void conv_vec_kernel(const T* __restrict__ in, int ld, const float* _
       const float4 u = *reinterpret_cast<const float4*>(w + (size_t)c * NT + i);
       wv[i] = u.x; wv[i + 1] = u.y; wv[i + 2] = u.z; wv[i + 3] = u.w;
     }
+    bool same[NT];
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
-      const int sp = pos - (NT - 1) + j;
+      const int back = NT - 1 - j;
+      same[j] = back == 0 || (t - back >= 0 && token_req[t - back] == r);
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const int back = NT - 1 - j;
       float x[VEC];
-      if (sp >= start) {
-        Vec16<T>::load(in + (size_t)(row0 + sp - start) * ld + c, x);
-      } else if (sp >= 0) {
-        const float* tp = tail + (size_t)(sp - (start - (NT - 1))) * C + c;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) x[e] = tp[e];
-      } else {
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) x[e] = 0.f;
-      }
+      if (same[j]) Vec16<T>::load(in + (size_t)(t - back) * ld + c, x);
+      else older(back, x);
 #pragma unroll
       for (int e = 0; e < VEC; ++e) acc[e] = fmaf(wv[e * NT + j], x[e], acc[e]);
     }
   } else {
     for (int j = 0; j < taps; ++j) {
-      const int sp = pos - (taps - 1) + j;
-      if (sp < 0) continue;
+      const int back = taps - 1 - j;
       float x[VEC];
-      if (sp >= start) {
-        Vec16<T>::load(in + (size_t)(row0 + sp - start) * ld + c, x);
-      } else {
-        const float* tp = tail + (size_t)(sp - (start - (taps - 1))) * C + c;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) x[e] = tp[e];
-      }
+      if (back == 0 || (t - back >= 0 && token_req[t - back] == r)) Vec16<T>::load(in + (size_t)(t - back) * ld + c, x);
+      else older(back, x);
 #pragma unroll
       for (int e = 0; e < VEC; ++e) acc[e] = fmaf(w[(size_t)(c + e) * taps + j], x[e], acc[e]);
     }

@@ -16,13 +16,14 @@
 
 #include <math_constants.h>
 
-constexpr int kRouteWarps = 4;
+constexpr int kRouteWarps = 8;
 constexpr int kRouteTokens = 8;        // tokens a block routes at most: a router row is fetched once for all of them
 
 // A block takes `tb` consecutive tokens (1, 2, 4 or 8, as many as their inputs fit shared memory).  Logits: warp w
-// makes those of the experts e = w, w + 4, ...: its lanes walk the row of W_r once (lane l the columns l, l + 32, ...)
-// and keep one sum per token; the lanes' sums are then added across the warp.  A token's sums are taken in an order
-// that depends on K only.  Then warp w chooses for the tokens w, w + 4, ...
+// takes the w-th slice of K for every expert (two experts at a time, every load of the slice requested before the
+// first is used); its lanes walk the slice (lane l the columns l, l + 32, ...) and keep one sum per token and expert,
+// the lanes' sums are added across the warp, and the warps' sums in the order of the warps.  A token's sums are
+// therefore taken in an order that depends on K only.  Then warp w chooses for the tokens w, w + 8, ...
 template <typename T>
 __global__ void __launch_bounds__(kRouteWarps * 32)
 route_kernel(const T* __restrict__ h, int ld_h, const float* __restrict__ w_router, const float* __restrict__ logits,
@@ -37,7 +38,8 @@ route_kernel(const T* __restrict__ h, int ld_h, const float* __restrict__ w_rout
   const int n_all = E + n_identity;
   float* s_all = smem;                                  // [tb][n_all] logits, then scores
   float* c_all = s_all + (size_t)tb * n_all;            // [tb][n_all] choice scores; -inf once chosen
-  float* x = c_all + (size_t)tb * n_all;                // [tb][K] the tokens' inputs, float32 (not with logits)
+  float* part_all = c_all + (size_t)tb * n_all;         // [kRouteWarps][tb][n_all] the warps' sums (not with logits)
+  float* x = part_all + (size_t)kRouteWarps * tb * n_all;   // [tb][K] the tokens' inputs, float32 (not with logits)
   if (logits != nullptr) {
     for (int i = threadIdx.x; i < n_tok * n_all; i += blockDim.x) s_all[i] = logits[(size_t)t0 * n_all + i];
   } else {
@@ -47,24 +49,42 @@ route_kernel(const T* __restrict__ h, int ld_h, const float* __restrict__ w_rout
     }
     for (int i = threadIdx.x + n_tok * K; i < tb * K; i += blockDim.x) x[i] = 0.f;
     __syncthreads();
-    for (int e = warp; e < n_all; e += kRouteWarps) {
-      const float* wr = w_router + (size_t)e * K;
-      float part[kRouteTokens];
+    const int slice = ((K + kRouteWarps - 1) / kRouteWarps + 31) / 32 * 32;
+    const int k0 = warp * slice, k1 = min(K, k0 + slice);
+    for (int e0 = 0; e0 < n_all; e0 += 2) {
+      const bool two = e0 + 1 < n_all;
+      const float* wr0 = w_router + (size_t)e0 * K;
+      const float* wr1 = w_router + (size_t)(two ? e0 + 1 : e0) * K;
+      float p0[kRouteTokens], p1[kRouteTokens];
 #pragma unroll
-      for (int tt = 0; tt < kRouteTokens; ++tt) part[tt] = 0.f;
-#pragma unroll 4
-      for (int k = lane; k < K; k += 32) {
-        const float wv = wr[k];
+      for (int tt = 0; tt < kRouteTokens; ++tt) { p0[tt] = 0.f; p1[tt] = 0.f; }
+#pragma unroll 8
+      for (int k = k0 + lane; k < k1; k += 32) {
+        const float a = wr0[k], b = wr1[k];
 #pragma unroll
-        for (int tt = 0; tt < kRouteTokens; ++tt)
-          if (tt < tb) part[tt] = fmaf(wv, x[tt * K + k], part[tt]);
+        for (int tt = 0; tt < kRouteTokens; ++tt) {
+          if (tt < tb) {
+            const float xv = x[tt * K + k];
+            p0[tt] = fmaf(a, xv, p0[tt]);
+            p1[tt] = fmaf(b, xv, p1[tt]);
+          }
+        }
       }
 #pragma unroll
       for (int tt = 0; tt < kRouteTokens; ++tt) {
         if (tt >= tb) break;
-        const float z = warp_sum(part[tt]);
-        if (lane == 0) s_all[tt * n_all + e] = z;
+        const float z0 = warp_sum(p0[tt]), z1 = warp_sum(p1[tt]);
+        if (lane == 0) {
+          part_all[((size_t)warp * tb + tt) * n_all + e0] = z0;
+          if (two) part_all[((size_t)warp * tb + tt) * n_all + e0 + 1] = z1;
+        }
       }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < tb * n_all; i += blockDim.x) {
+      float z = 0.f;
+      for (int w = 0; w < kRouteWarps; ++w) z += part_all[(size_t)w * tb * n_all + i];
+      s_all[i] = z;
     }
   }
   __syncthreads();
@@ -134,8 +154,10 @@ KVB_EXPORT int kvb_route(const void* h, int ld_h, const float* w_router, const f
   const int n_all = E + n_identity;
   // as many tokens a block as their inputs fit 160 KB with, 8 at most; few tokens are spread over more blocks
   int tb = kRouteTokens;
-  const size_t x_floats = logits ? 0 : (size_t)K;
+  const size_t x_floats = logits ? 0 : (size_t)K + (size_t)kRouteWarps * n_all;
+  // half of that once the step has blocks enough to fill the GPU either way: more blocks per SM hide more latency
   while (tb > 1 && ((size_t)tb * (x_floats + 2 * n_all) * sizeof(float) > 160 * 1024 || (T_ + tb - 1) / tb < 64)) tb >>= 1;
+  if (tb == kRouteTokens && T_ / (tb / 2) >= 4 * kvb_sm_count()) tb >>= 1;
   const size_t smem = (size_t)tb * (x_floats + 2 * n_all) * sizeof(float);
   if (smem > 200 * 1024) return KVB_ERR_BAD_SIZE;
   KVB_DISPATCH_DTYPE(dtype, T, {
@@ -170,11 +192,49 @@ __global__ void expert_act_kernel(const T* __restrict__ p, const float* __restri
   }
 }
 
+// bfloat16 rows whose experts are multiples of 8 features wide: eight elements per thread, 16-byte accesses, one
+// look at the token's weight for the expert.
+__global__ void expert_act_bf16x8_kernel(const __nv_bfloat16* __restrict__ p, const float* __restrict__ gate, int ld_gate,
+                                         __nv_bfloat16* __restrict__ out, int EF, int F, int width, size_t groups) {
+  pdl_trigger();
+  pdl_wait();
+  const int gpr = width >> 3;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / gpr;
+    const int j = (int)(idx - t * gpr) << 3;
+    const float g = j < EF ? gate[t * ld_gate + j / F] : 1.f;
+    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+    if (g != 0.f) {
+      const uint4 u = *reinterpret_cast<const uint4*>(p + t * width + j);
+      const unsigned w[4] = {u.x, u.y, u.z, u.w};
+      unsigned r[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float a = fmaxf(__uint_as_float(w[k] << 16), 0.f), b = fmaxf(__uint_as_float(w[k] & 0xffff0000u), 0.f);
+        __nv_bfloat162 v = __floats2bfloat162_rn(a * a * g, b * b * g);
+        r[k] = *reinterpret_cast<unsigned*>(&v);
+      }
+      o = make_uint4(r[0], r[1], r[2], r[3]);
+    }
+    *reinterpret_cast<uint4*>(out + t * width + j) = o;
+  }
+}
+
 KVB_EXPORT int kvb_expert_act(const void* p, const float* gate, int ld_gate, void* out, int T_, int E, int F, int S,
                               int dtype, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   const int width = E * F + S;
   if (E < 0 || F < 1 || S < 0 || width < 1) return KVB_ERR_BAD_SIZE;
+  if (dtype == KVB_BF16 && F % 8 == 0 && S % 8 == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    const size_t groups = (size_t)T_ * (width / 8);
+    const size_t want8 = (groups + 255) / 256;
+    const int blocks8 = (int)(want8 < (size_t)kvb_sm_count() * 16 ? want8 : (size_t)kvb_sm_count() * 16);
+    kvb_launch(expert_act_bf16x8_kernel, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)p, gate, ld_gate,
+               (__nv_bfloat16*)out, E * F, F, width, groups);
+    return kvb_launch_result();
+  }
   const size_t total = (size_t)T_ * width;
   const size_t want = (total + 255) / 256;
   const int blocks = (int)(want < (size_t)kvb_sm_count() * 16 ? want : (size_t)kvb_sm_count() * 16);
