@@ -236,8 +236,10 @@ __device__ __forceinline__ void load_16_bytes(const __nv_bfloat16* p, float* x) 
   for (int e = 0; e < 4; ++e) { x[2 * e] = __uint_as_float(w[e] << 16); x[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u); }
 }
 
+// Small groups and values keep to 64 registers, so that four blocks share an SM (a decode step of 64 requests and
+// 8 key/value heads is then one round of blocks, not one and a seventh).
 template <typename T, int VPL, int GP>
-__global__ void __launch_bounds__(kGroupWarps * 32)
+__global__ void __launch_bounds__(kGroupWarps * 32, (GP * VPL <= 8) ? 4 : 1)
 window_attention_group_kernel(const T* __restrict__ q_base, int q_row_stride, const T* __restrict__ pages,
                               const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
                               const int* __restrict__ positions, const int* __restrict__ token_req, T* __restrict__ out,
