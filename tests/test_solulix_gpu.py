@@ -630,3 +630,53 @@ def test_replay_through_the_trace_runner(dtype, flags):
                 step += 1
     finally:
         tr.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_are_no_multiples_of_eight(dtype):
+    """A width of 36, heads of 5, 3 and 7 channels, experts 6 wide, 50 tokens in the vocabulary: nothing may rest on
+    16-byte rows.  Whole, in portions and token by token."""
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    folder = tempfile.mkdtemp(prefix="kvb200_sx_")
+    layers = [tiny.attention(heads=3, kv_heads=1, dim=5, vdim=3, conv=2, scale=0.4, size=7, keep_first=2,
+                             mlp=tiny.moe(experts=3, identity=1, top=2, scale=1.1, ff=6, shared=10)),
+              tiny.delta(heads=3, kv_heads=3, dim=7, vdim=5, conv=3, mlp=tiny.dense(18))]
+    cfg = tiny.config(layers, width=36, vocab=50, loop={"start": 0, "stop": 2, "times": 2})
+    w = tiny.write_model(folder, cfg, seed=3)
+    r = _runner(folder, dtype)
+    seq = np.random.default_rng(3).integers(0, 50, 40).tolist()
+    ref = S.forward(cfg, w, seq)
+    got, pos = [], 0
+    for n in (13, 2, 21, 1, 1, 1, 1):
+        got.append(r.step([StepEntry(0, seq[pos:pos + n], pos, range(n))]).cpu().numpy())
+        pos += n
+    assert _logit_err(np.concatenate(got), ref, dtype) < TOL_MODEL[dtype]
+    r.check_status()
+
+
+def test_command_line_serves_the_design():
+    """The engine's command line on a Solulix folder: requests on standard input in the wire format, greedy tokens
+    back as JSON lines; each token is the plain model's best (ties within 1e-4 allowed)."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    folder = tempfile.mkdtemp(prefix="kvb200_sx_")
+    cfg = tiny.MIXED
+    w = tiny.write_model(folder, cfg, seed=8)
+    rng = np.random.default_rng(4)
+    prompts = {3: rng.integers(0, cfg["vocab"], 9).tolist(), 11: rng.integers(0, cfg["vocab"], 26).tolist()}
+    lines = [f"{rid} 6 1 " + " ".join(map(str, toks)) for rid, toks in prompts.items()]
+    env = dict(os.environ, IGNORE_EOS="1", PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    p = subprocess.run([sys.executable, "-m", "kv_cache_optimization_for_llm_b200.cli", folder, "--dtype", "float32",
+                        "--page-size", "4", "--num-pages", "64", "--max-num-seqs", "4", "--max-model-len", "64"],
+                       input="\n".join(lines) + "\n", capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    out = [json.loads(line) for line in p.stdout.splitlines() if line.strip()]
+    for rid, prompt in prompts.items():
+        toks = [m["tok"] for m in out if m.get("id") == rid and "tok" in m]
+        assert len(toks) == 6
+        logits = S.forward(cfg, w, prompt + toks)
+        for j, tok in enumerate(toks):
+            row = logits[len(prompt) + j - 1]
+            assert row[tok] >= row.max() - 1e-4 * np.abs(row).max(), (rid, j)
