@@ -425,11 +425,11 @@ def rezusun_config(z):
 def solulix_config(z, window=1024, keep_first=64):
     """Six layers at the comparison's sizes: attention (heads of 64, a quarter as many key/value heads, four taps, a
     window of 1024 tokens that keeps the first 64) and the gated delta rule (heads of 64 x 64) in turn; dense
-    feed-forwards of the same width as Llama's, and on every third layer 16 experts of an eighth of that width of
-    which a token uses two, two identity experts and a shared expert of a quarter."""
+    feed-forwards of the same width as Llama's, and on every third layer 32 experts of a sixteenth of that width of
+    which a token uses four, one identity expert and a shared expert of a quarter."""
     dense = {"kind": "dense", "ff": z["ff"]}
-    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 8}, "shared": {"ff": z["ff"] // 4},
-           "router": {"experts": 16, "identity": 2, "top": 2, "scale": 2.0}}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 16}, "shared": {"ff": z["ff"] // 4},
+           "router": {"experts": 32, "identity": 1, "top": 4, "scale": 2.5}}
     att = {"heads": z["heads"], "kv_heads": z["heads"] // 4, "dim": 64, "vdim": 64, "conv": 4, "scale": 0.125,
            "mask": {"size": window, "keep_first": keep_first}}
     dlt = {"heads": z["heads"], "kv_heads": z["heads"] // 4, "dim": 64, "vdim": 64, "conv": 4}
@@ -540,7 +540,7 @@ def run_compare_solulix(size):
     seen = sum(min(i + 1, window) + max(0, min(keep, i + 1 - window)) for i in range(T))
     H, G, W = z["heads"], z["heads"] // 4, z["width"]
     channels = (H + 2 * G) * 64
-    n_cols = 16 * (z["ff"] // 8) + z["ff"] // 4
+    n_cols = 32 * (z["ff"] // 16) + z["ff"] // 4
 
     def per_launch(d, phase, key, *names):
         for name in names:
@@ -578,7 +578,7 @@ def run_compare_solulix(size):
         "solulix expert_act, 2048 tokens (of the measured copy peak)": frac(
             T * n_cols * 4, per_launch(sol, "prefill_2048", "operators", "expert_act"), hbm),
         "solulix route, 2048 tokens (of the nominal fp32 FMA peak)": frac(
-            T * 18 * W * 2, per_launch(sol, "prefill_2048", "operators", "route"), fma),
+            T * 33 * W * 2, per_launch(sol, "prefill_2048", "operators", "route"), fma),
     }
     return {"compare": size, "design": "solulix", "sizes": z, "window": window, "keep_first": keep, "dtype": "bf16",
             "data": "synthetic", "peaks": pk, "llama": llama, "solulix": sol, "kernel_roofline_fractions": kernels,
