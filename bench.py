@@ -563,10 +563,9 @@ def run_compare_solulix(size):
             R * min(ctx, window + keep) * 2 * G * 64 * 2, per_launch(sol, "decode_b64", "operators_launched", "window_attention"), hbm),
         "llama rope_kv_write, 2048 tokens (of the measured copy peak)": frac(
             T * (2 * channels + 2 * G * 64) * 2, per_launch(llama, "prefill_2048", "operators", "rope_kv_write"), hbm),
+        # the convolution also writes the keys and values into their pages
         "solulix conv_silu, 2048 tokens (of the measured copy peak)": frac(
             T * 2 * channels * 2, per_launch(sol, "prefill_2048", "operators", "conv_silu"), hbm),
-        "solulix kv_rows_append, 2048 tokens (of the measured copy peak)": frac(
-            T * 2 * 2 * G * 64 * 2, per_launch(sol, "prefill_2048", "operators", "kv_rows_append"), hbm),
         "solulix delta_scan, 2048 tokens (of the nominal fp32 FMA peak)": frac(
             T * H * 64 * 64 * 10, per_launch(sol, "prefill_2048", "operators", "delta_scan"), fma),
         "solulix delta_scan, batch 64 (of the measured copy peak)": frac(
